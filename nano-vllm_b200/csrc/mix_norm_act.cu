@@ -24,11 +24,14 @@ __global__ void __launch_bounds__(ROW_THREADS) embed_kernel(const int64_t* __res
 
 // Norm on a sublayer's OUTPUT, then the residual update:  x[row] += mult * y[row] / sqrt(mean(y^2) + eps) * (w_offset + w).
 // y is the branch output in the activation type, or (y32) in fp32.  `copy`, when given, receives the updated row in the
-// activation type: the operand of the next sublayer's projections, which read the stream itself.
+// activation type: the operand of the next sublayer's projections, which read the stream itself.  `out_next`, when given,
+// receives the RMS norm of the updated row with the next sublayer's input weight, x / sqrt(mean(x^2) + eps) * (next_offset +
+// w_next): layers that norm a sublayer on both sides do the closing norm, the update and the opening norm in one pass.
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS) add_normed_kernel(float* __restrict__ x, const T* __restrict__ y,
                                                                  const float* __restrict__ y32, const T* __restrict__ w, float mult,
-                                                                 float w_offset, T* __restrict__ copy, int cols, float eps) {
+                                                                 float w_offset, T* __restrict__ copy, const T* __restrict__ w_next,
+                                                                 float next_offset, T* __restrict__ out_next, int cols, float eps) {
     B200_PDL_SYNC();
     __shared__ float red[ROW_THREADS / 32];
     const int64_t base = (int64_t)blockIdx.x * cols;
@@ -38,12 +41,75 @@ __global__ void __launch_bounds__(ROW_THREADS) add_normed_kernel(float* __restri
         q = fmaf(v, v, q);
     }
     const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)cols + eps);
+    float q2 = 0.f;
     for (int c = threadIdx.x; c < cols; c += blockDim.x) {
         const float v = y32 ? y32[base + c] : ldf(y + base + c);
         const float r = fmaf(mult, v * rstd * (w_offset + ldf(w + c)), x[base + c]);
         x[base + c] = r;
+        q2 = fmaf(r, r, q2);
         if (copy) stf(copy + base + c, r);
     }
+    if (out_next == nullptr) return;
+    const float rstd2 = 1.0f / sqrtf(block_sum(q2, red) / (float)cols + eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x)      // the same thread wrote these elements: no fence needed
+        stf(out_next + base + c, x[base + c] * rstd2 * (next_offset + ldf(w_next + c)));
+}
+
+// Token embedding scaled by a constant, plus a hashed embedding of the (previous token, token) pair:
+//     x = table[id] * scale + pair[(prev * mul_prev + id * mul_cur) mod buckets],   row `buckets` of pair for a sequence's first token.
+// The previous token of a portion's first token comes from the sequence's state slot (prev_tok, int64 [slots]); afterwards
+// token_state_update_kernel leaves the portion's last token there.  One CTA per (token of a portion, sequence).
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS) embed_pair_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table, float scale,
+                                                                 const T* __restrict__ pair, int64_t buckets, int64_t mul_prev,
+                                                                 int64_t mul_cur, const int64_t* __restrict__ prev_tok,
+                                                                 const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q,
+                                                                 const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
+                                                                 float* __restrict__ out, T* __restrict__ copy, int width, int64_t vocab) {
+    B200_PDL_SYNC();
+    const int s = blockIdx.y, i = blockIdx.x;
+    const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+    if (cu_q == nullptr && sp.qlen == 0) {                 // padding row of a captured single-token step: defined, unused
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            out[(int64_t)s * width + c] = 0.f;
+            if (copy) stf(copy + (int64_t)s * width + c, 0.f);
+        }
+        return;
+    }
+    if (i >= sp.qlen) return;
+    const int64_t row = sp.q0 + i;
+    const int pos = sp.klen - sp.qlen + i;
+    int64_t id = ids[row];
+    if (id < 0 || id >= vocab) id = 0;
+    const T* src = table + id * width;
+    const T* src2 = nullptr;
+    if (pair != nullptr) {
+        int64_t prow = buckets;
+        if (pos > 0) {
+            int64_t prev = i > 0 ? ids[row - 1] : prev_tok[state_slots[s]];
+            if (prev < 0 || prev >= vocab) prev = 0;
+            prow = (prev * mul_prev + id * mul_cur) % buckets;
+            if (prow < 0) prow += buckets;
+        }
+        src2 = pair + prow * width;
+    }
+    float* dst = out + row * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = ldf(src + c) * scale;
+        if (src2) v += ldf(src2 + c);
+        dst[c] = v;
+        if (copy) stf(copy + row * width + c, v);
+    }
+}
+
+__global__ void token_state_update_kernel(const int64_t* __restrict__ ids, int64_t* __restrict__ prev_tok,
+                                          const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q,
+                                          const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, int num_seqs) {
+    B200_PDL_SYNC();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= num_seqs) return;
+    const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+    if (sp.qlen > 0) prev_tok[state_slots[s]] = ids[sp.q0 + sp.qlen - 1];
 }
 
 // out[i] = x[row] / sqrt(mean(x[row]^2) + eps) * (w_offset + w) for row = rows_idx[i] (or i) of an fp32 stream.
@@ -121,7 +187,7 @@ __device__ __forceinline__ float gelu_tanh_(float z) {
 }
 
 // kind 0: x = [gate | up] per row, out = gelu_tanh(gate) * up;  kind 1: out = relu(x)^2 (no second half);
-// kind 2: x = [gate | up], out = silu(gate) * up
+// kind 2: x = [gate | up], out = silu(gate) * up;  kind 3: out = gelu_tanh(x) (no second half)
 template <typename T>
 __global__ void ff_act_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int n, int kind) {
     B200_PDL_SYNC();
@@ -132,6 +198,8 @@ __global__ void ff_act_kernel(const T* __restrict__ x, T* __restrict__ out, int6
     if (kind == 1) {
         const float v = fmaxf(ldf(x + i), 0.f);
         stf(out + i, v * v);
+    } else if (kind == 3) {
+        stf(out + i, gelu_tanh_(ldf(x + i)));
     } else {
         const float g = ldf(x + r * 2 * n + c), u = ldf(x + r * 2 * n + n + c);
         stf(out + i, (kind == 0 ? gelu_tanh_(g) : siluf_(g)) * u);
@@ -145,13 +213,13 @@ __global__ void __launch_bounds__(256) ff_act_vec_kernel(const __nv_bfloat16* __
     if (c >= n) return;
     const int64_t r = blockIdx.y;
     float o[8];
-    if (kind == 1) {
+    if (kind == 1 || kind == 3) {
         float v[8];
         unpack8(*reinterpret_cast<const uint4*>(x + r * n + c), v);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const float t = fmaxf(v[e], 0.f);
-            o[e] = t * t;
+            o[e] = kind == 1 ? t * t : gelu_tanh_(v[e]);
         }
     } else {
         float gt[8], up[8];
@@ -165,7 +233,7 @@ __global__ void __launch_bounds__(256) ff_act_vec_kernel(const __nv_bfloat16* __
 
 }  // namespace
 
-extern "C" int b200m_abi_version(void) { return 2; }
+extern "C" int b200m_abi_version(void) { return 3; }
 
 extern "C" int b200m_embed(const int64_t* ids, const void* table, float* out, void* copy, int n, int width, int64_t vocab, int is32,
                            void* stream) {
@@ -182,7 +250,37 @@ extern "C" int b200m_add_normed(float* x, const void* y, const float* y32, const
     if (rows == 0) return B200_OK;
     B200M_DISPATCH(is32, B200_LAUNCH((add_normed_kernel<T>), rows, ROW_THREADS, 0, static_cast<cudaStream_t>(stream), x,
                                      static_cast<const T*>(y), y32, static_cast<const T*>(w), mult, w_offset,
-                                     static_cast<T*>(copy), cols, eps));
+                                     static_cast<T*>(copy), static_cast<const T*>(nullptr), 0.f, static_cast<T*>(nullptr), cols, eps));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_add_normed_norm(float* x, const void* y, const float* y32, const void* w, float mult, float w_offset, void* copy,
+                                     const void* w_next, float next_offset, void* out_next, int rows, int cols, float eps, int is32,
+                                     void* stream) {
+    if (!x || (!y && !y32) || !w || rows < 0 || cols <= 0 || (out_next && !w_next)) return B200_EINVAL;
+    if (rows == 0) return B200_OK;
+    B200M_DISPATCH(is32, B200_LAUNCH((add_normed_kernel<T>), rows, ROW_THREADS, 0, static_cast<cudaStream_t>(stream), x,
+                                     static_cast<const T*>(y), y32, static_cast<const T*>(w), mult, w_offset,
+                                     static_cast<T*>(copy), static_cast<const T*>(w_next), next_offset, static_cast<T*>(out_next),
+                                     cols, eps));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_embed_pair(const int64_t* ids, const void* table, float scale, const void* pair, int64_t buckets, int64_t mul_prev,
+                                int64_t mul_cur, int64_t* prev_tok, const int32_t* state_slots, const int32_t* cu_q,
+                                const int32_t* cu_k, const int32_t* ctx_lens, float* out, void* copy, int num_seqs, int max_q, int width,
+                                int64_t vocab, int is32, void* stream) {
+    if (!ids || !table || !out || width <= 0 || vocab <= 0) return B200_EINVAL;
+    if (pair && (buckets <= 0 || !prev_tok || !state_slots)) return B200_EINVAL;
+    if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
+    if (num_seqs <= 0 || max_q <= 0) return B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    B200M_DISPATCH(is32, B200_LAUNCH((embed_pair_kernel<T>), dim3(max_q, num_seqs), ROW_THREADS, 0, st, ids, static_cast<const T*>(table),
+                                     scale, static_cast<const T*>(pair), buckets, mul_prev, mul_cur, prev_tok, state_slots, cu_q, cu_k,
+                                     ctx_lens, out, static_cast<T*>(copy), width, vocab));
+    int rc = b200_launch_status(nullptr);
+    if (rc != B200_OK || !pair) return rc;
+    B200_LAUNCH((token_state_update_kernel), (num_seqs + 127) / 128, 128, 0, st, ids, prev_tok, state_slots, cu_q, cu_k, ctx_lens, num_seqs);
     return b200_launch_status(nullptr);
 }
 
@@ -216,12 +314,12 @@ extern "C" int b200m_rmsnorm(const void* x, int64_t x_stride, const void* w, voi
 }
 
 extern "C" int b200m_ff_act(const void* x, void* out, int64_t rows, int n, int kind, int is32, void* stream) {
-    if (!x || !out || rows < 0 || n <= 0 || kind < 0 || kind > 2) return B200_EINVAL;
+    if (!x || !out || rows < 0 || n <= 0 || kind < 0 || kind > 3) return B200_EINVAL;
     if (rows == 0) return B200_OK;
     if (!is32 && n % 8 == 0 && rows <= 65535 * 32 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
         for (int64_t r0 = 0; r0 < rows; r0 += 65535) {             // grid.y limit
             const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
-            const int64_t in_row = kind == 1 ? n : 2 * (int64_t)n;
+            const int64_t in_row = (kind == 1 || kind == 3) ? n : 2 * (int64_t)n;
             B200_LAUNCH((ff_act_vec_kernel), dim3((n / 8 + 255) / 256, (unsigned)nr), 256, 0, static_cast<cudaStream_t>(stream),
                         static_cast<const __nv_bfloat16*>(x) + r0 * in_row, static_cast<__nv_bfloat16*>(out) + r0 * n, n, kind);
         }

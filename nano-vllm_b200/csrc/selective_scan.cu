@@ -6,7 +6,7 @@
 // A step whose sequence has no tokens behind it starts from zeros whatever the slot holds, so a slot needs no clearing
 // when it changes hands.
 //
-//   causal_conv_kernel      : depthwise causal convolution + bias + SiLU over a varlen batch, history taken from the slot
+//   causal_conv_kernel      : depthwise causal convolution + bias (+ SiLU) over a varlen batch, history taken from the slot
 //   conv_state_update_kernel: the slot's history after the step (run after the convolution: it overwrites what that reads)
 //   selective_scan_kernel   : the recurrence, serial over a sequence's tokens, 4 lanes per channel holding the state in
 //                             registers; one token per sequence is the decode case of the same kernel.  Long portions run
@@ -25,7 +25,7 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
                                                           const T* __restrict__ bias, const float* __restrict__ conv_state,
                                                           const int32_t* __restrict__ state_slots, const int32_t* __restrict__ cu_q,
                                                           const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
-                                                          T* __restrict__ out, int channels, int taps, int tok_tile) {
+                                                          T* __restrict__ out, int channels, int taps, int tok_tile, int act) {
     B200_PDL_SYNC();
     const int s = blockIdx.z;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
             float a = b;
 #pragma unroll
             for (int k = 0; k < CONV_MAX_TAPS; ++k) a = fmaf(wr[k], win[k], a);
-            stf(out + (int64_t)(sp.q0 + i) * channels + c, siluf_(a));
+            stf(out + (int64_t)(sp.q0 + i) * channels + c, act ? siluf_(a) : a);
 #pragma unroll
             for (int k = CONV_MAX_TAPS - 1; k >= 1; --k) win[k] = win[k - 1];
         }
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
     for (int i = i0; i < i1; ++i) {
         float a = b;
         for (int k = 0; k < taps; ++k) a = fmaf(ldf(w + (int64_t)c * taps + k), input(i - (taps - 1 - k)), a);
-        stf(out + (int64_t)(sp.q0 + i) * channels + c, siluf_(a));
+        stf(out + (int64_t)(sp.q0 + i) * channels + c, act ? siluf_(a) : a);
     }
 }
 
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(256) scan_carry_kernel(const float* __restrict
 
 extern "C" int b200m_causal_conv(const void* x, int64_t x_stride, const void* w, const void* bias, float* conv_state,
                                  const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
-                                 void* out, int num_seqs, int max_q, int channels, int taps, int is32, void* stream) {
+                                 void* out, int num_seqs, int max_q, int channels, int taps, int act, int is32, void* stream) {
     if (!x || !w || !conv_state || !state_slots || !out || channels <= 0 || taps <= 0) return B200_EINVAL;
     if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
     if (num_seqs <= 0 || max_q <= 0) return B200_OK;
@@ -319,7 +319,7 @@ extern "C" int b200m_causal_conv(const void* x, int64_t x_stride, const void* w,
     dim3 grid((channels + 255) / 256, (max_q + tok_tile - 1) / tok_tile, num_seqs);
     B200M_DISPATCH(is32, B200_LAUNCH((causal_conv_kernel<T>), grid, 256, 0, st, static_cast<const T*>(x), x_stride,
                                      static_cast<const T*>(w), static_cast<const T*>(bias), conv_state, state_slots, cu_q, cu_k,
-                                     ctx_lens, static_cast<T*>(out), channels, taps, tok_tile));
+                                     ctx_lens, static_cast<T*>(out), channels, taps, tok_tile, act));
     int rc = b200_launch_status(nullptr);
     if (rc != B200_OK || taps == 1) return rc;
     dim3 grid2((channels + 255) / 256, num_seqs);

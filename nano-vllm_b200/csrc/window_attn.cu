@@ -2,8 +2,9 @@
 //
 // Per token the cache holds one row [k (G * dim) | v (G * vdim)] per layer that owns a key/value projection; query head h
 // reads key/value head h / (H / G).  There is no rotation: position enters through the bias and the window only.
-//     s_ij = (q_i . k_j) * scale - slope[h] * (i - j),   visible: 0 <= i - j < window   (window <= 0: every j <= i)
+//     s_ij = (q_i . k_j) * scale - slope[h] * (i - j),   visible: 0 <= i - j < window or j < keep_first   (window <= 0: every j <= i)
 //     p = softmax over the visible j,   out_i = sum_j p_ij v_j
+// The kernels read whatever the cache rows hold: a design that rotates its keys stores them rotated (headnorm_rope_store_kernel).
 // Softmax statistics and the output accumulate in fp32 in both element types.
 //
 //   qk_norm_store_kernel : RMS norm of the WHOLE query projection and of the whole key projection (one statistic per token
@@ -98,14 +99,18 @@ __global__ void __launch_bounds__(256) qk_norm_store_vec_kernel(__nv_bfloat16* _
 
 // One warp per (token, head-in-group) pair; a CTA covers WA_WARPS consecutive pairs of one sequence and one key/value head.
 // OACC = ceil(vdim / 32): output accumulators per lane.
+// keep_first > 0 (with a window): the first keep_first tokens of a sequence stay visible to every later token; the CTA walks
+// those keys first, then the keys of its window.  vsets > 1: every query head's weights are applied to the values of each of
+// the vsets (= G) value heads in turn (blockIdx.z names the pair), giving out [total_q, H, vsets, vdim]: what a mixing of the
+// heads' weight matrices after the softmax needs.  out32 != nullptr: the result is written there in fp32 instead.
 template <typename T, int OACC>
 __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
     const T* __restrict__ q, int64_t q_stride,        // [total_q, >= H * dim]
     const T* __restrict__ cache, int row_elems, int v_off,
     const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
     const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
-    const float* __restrict__ slopes, int window,
-    T* __restrict__ out,                              // [total_q, H * vdim]
+    const float* __restrict__ slopes, int window, int keep_first, int vsets,
+    T* __restrict__ out, float* __restrict__ out32,   // [total_q, H * vsets * vdim]
     int H, int G, int dim, int vdim, float scale) {
     B200_PDL_SYNC();
     extern __shared__ float smem[];
@@ -114,7 +119,8 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
     float* tile = smem;                                    // [WA_TILE][DS]: k (dim) | v (vdim) of one key/value head
     float* qs = tile + WA_TILE * DS;                       // [WA_WARPS][dim]
     float* pb = qs + WA_WARPS * dim;                       // [WA_WARPS][WA_TILE]
-    const int s = blockIdx.y, g = blockIdx.z, rep = H / G;
+    const int s = blockIdx.y, g = blockIdx.z / vsets, rep = H / G;
+    const int vs = blockIdx.z - g * vsets, vh = vsets > 1 ? vs : g;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int npairs = sp.qlen * rep;
@@ -126,8 +132,9 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
     const int first = sp.klen - sp.qlen;                   // position of this step's first token
     const int pos = first + i;
     const int i_lo = pair0 / rep, i_hi = min(sp.qlen - 1, (pair0 + WA_WARPS - 1) / rep);
-    const int kmax = first + i_hi + 1;                     // keys any warp of this CTA may see: [kmin, kmax)
+    const int kmax = first + i_hi + 1;                     // keys any warp of this CTA may see: [0, nkeep) and [kmin, kmax)
     const int kmin = window > 0 ? max(0, first + i_lo - window + 1) : 0;
+    const int nkeep = min(keep_first, kmin);
     const int my_lo = window > 0 ? max(0, pos - window + 1) : 0;
     float* myq = qs + warp * dim;
     if (active) {
@@ -140,20 +147,23 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
 #pragma unroll
     for (int k = 0; k < OACC; ++k) acc[k] = 0.f;
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
-    for (int j0 = kmin; j0 < kmax; j0 += WA_TILE) {
+    const int nwalk = nkeep + (kmax - kmin);               // walked keys: index u < nkeep is key u, else key kmin + (u - nkeep)
+    for (int u0 = 0; u0 < nwalk; u0 += WA_TILE) {
         __syncthreads();                                   // previous tile consumed (and the queries written)
-        const int rows = min(WA_TILE, kmax - j0);
+        const int rows = min(WA_TILE, nwalk - u0);
         for (int e = threadIdx.x; e < rows * D; e += blockDim.x) {
             const int r = e / D, c = e - r * D;
-            const int j = j0 + r;
+            const int u = u0 + r;
+            const int j = u < nkeep ? u : kmin + (u - nkeep);
             const int64_t slot = (int64_t)bt[j / block_size] * block_size + (j % block_size);
             const T* src = cache + slot * row_elems;
-            tile[r * DS + c] = ldf(c < dim ? src + (int64_t)g * dim + c : src + v_off + (int64_t)g * vdim + (c - dim));
+            tile[r * DS + c] = ldf(c < dim ? src + (int64_t)g * dim + c : src + v_off + (int64_t)vh * vdim + (c - dim));
         }
         __syncthreads();
-        if (active && j0 <= pos && j0 + rows > my_lo) {    // the tile holds at least one key this row sees
-            const int j = j0 + lane;
-            const bool valid = lane < rows && j <= pos && j >= my_lo;
+        const int u = u0 + lane;
+        const int j = u < nkeep ? u : kmin + (u - nkeep);
+        const bool valid = active && lane < rows && j <= pos && (j >= my_lo || j < keep_first);
+        if (__any_sync(0xffffffffu, valid)) {              // the tile holds at least one key this row sees
             float sc = -INFINITY;
             if (valid) {
                 const float* kr = tile + lane * DS;
@@ -168,13 +178,12 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
             m = m_new;
             pb[warp * WA_TILE + lane] = p;
             __syncwarp();
-            const int r_lo = max(0, my_lo - j0), r_hi = min(rows, pos - j0 + 1);
 #pragma unroll
             for (int k = 0; k < OACC; ++k) {
                 const int c = lane + 32 * k;
                 float a = acc[k] * alpha;
                 if (c < vdim)
-                    for (int r = r_lo; r < r_hi; ++r) a = fmaf(pb[warp * WA_TILE + r], tile[r * DS + dim + c], a);
+                    for (int r = 0; r < rows; ++r) a = fmaf(pb[warp * WA_TILE + r], tile[r * DS + dim + c], a);
                 acc[k] = a;
             }
             __syncwarp();
@@ -182,11 +191,14 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(
     }
     if (active) {
         const float inv = 1.0f / l;
-        T* o = out + ((int64_t)(sp.q0 + i) * H + h) * vdim;
+        const int64_t o = (((int64_t)(sp.q0 + i) * H + h) * vsets + vs) * vdim;
 #pragma unroll
         for (int k = 0; k < OACC; ++k) {
             const int c = lane + 32 * k;
-            if (c < vdim) stf(o + c, acc[k] * inv);
+            if (c < vdim) {
+                if (out32) out32[o + c] = acc[k] * inv;
+                else stf(out + o + c, acc[k] * inv);
+            }
         }
     }
 }
@@ -206,16 +218,17 @@ int wa_ensure_smem(K kernel, size_t bytes) {
 template <typename T, int OACC>
 int launch_window_fma(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
                       int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
-                      const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, int dim, int vdim,
-                      float scale, cudaStream_t stream) {
+                      const float* slopes, int window, int keep_first, int vsets, void* out, bool out_f32, int num_seqs, int max_q,
+                      int H, int G, int dim, int vdim, float scale, cudaStream_t stream) {
     const int D = dim + vdim;
     const size_t smem = sizeof(float) * ((size_t)WA_TILE * (D | 1) + (size_t)WA_WARPS * dim + WA_WARPS * WA_TILE);
     int rc = wa_ensure_smem(window_attn_kernel<T, OACC>, smem);
     if (rc != B200_OK) return rc;
-    dim3 grid((max_q * (H / G) + WA_WARPS - 1) / WA_WARPS, num_seqs, G);
+    dim3 grid((max_q * (H / G) + WA_WARPS - 1) / WA_WARPS, num_seqs, G * vsets);
     B200_LAUNCH((window_attn_kernel<T, OACC>), grid, WA_WARPS * 32, smem, stream, static_cast<const T*>(q), q_stride,
                 static_cast<const T*>(cache), row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens, slopes,
-                window, static_cast<T*>(out), H, G, dim, vdim, scale);
+                window, keep_first, vsets, out_f32 ? nullptr : static_cast<T*>(out), out_f32 ? static_cast<float*>(out) : nullptr, H,
+                G, dim, vdim, scale);
     return b200_launch_status(nullptr);
 }
 
@@ -265,7 +278,8 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache, int row_elems, int v_off,
     const int32_t* __restrict__ block_tables, int bt_stride, int block_size, int bs_shift, const int32_t* __restrict__ cu_q,
     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, const float* __restrict__ slopes, int window,
-    __nv_bfloat16* __restrict__ out, int H, int G, float scale, int splits, float* __restrict__ part) {
+    int keep_first, int vsets, __nv_bfloat16* __restrict__ out, float* __restrict__ out32, int H, int G, float scale, int splits,
+    float* __restrict__ part) {
     static_assert(!KS || BN == 64, "the key-sharing form shares out 64-key tiles");
     B200_PDL_SYNC();
     constexpr int KSTR = DK + 8, VSTR = DV + 8;           // row strides: 16-byte multiples, odd in 16-byte units (conflict-free ldmatrix)
@@ -276,7 +290,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     __nv_bfloat16* Ks = Qs + BM * KSTR;                                  // [2][64][KSTR]
     __nv_bfloat16* Vs = Ks + 2 * BN * KSTR;                           // [2][64][VSTR]
     const int s = blockIdx.y, rep = H / G;
-    const int g = blockIdx.z / splits, split = blockIdx.z - g * splits;
+    const int gz = blockIdx.z / splits, split = blockIdx.z - gz * splits;
+    const int g = gz / vsets, vs = gz - g * vsets, vh = vsets > 1 ? vs : g;     // key head, value set, value head
+    const int HV = H * vsets;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     const int nrows = sp.qlen * rep;
     const int row0 = (gridDim.x - 1 - blockIdx.x) * BM;                  // the last rows of a portion see the most keys: launched first
@@ -286,27 +302,32 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     const int i_lo = row0 / rep, i_hi = min(sp.qlen - 1, (row0 + BM - 1) / rep);
     const int kmax = first + i_hi + 1;
     const int kmin = window > 0 ? max(0, first + i_lo - window + 1) : 0;
-    int t_lo = kmin / BN, t_hi = (kmax + BN - 1) / BN;          // key tiles [t_lo, t_hi)
+    const int t_lo = kmin / BN, t_hi = (kmax + BN - 1) / BN;    // key tiles of the window: [t_lo, t_hi)
+    // kept first tokens: their tiles below the window's are walked first.  Walked tile u is key tile u when u < n_keep, else
+    // key tile t_lo + (u - n_keep).
+    const int n_keep = (window > 0 && keep_first > 0) ? min((keep_first + BN - 1) / BN, t_lo) : 0;
+    int u_lo = 0, u_hi = n_keep + (t_hi - t_lo);
     if (splits > 1) {
-        const int nt = t_hi - t_lo;
-        const int a = t_lo + (int)(((int64_t)nt * split) / splits), b = t_lo + (int)(((int64_t)nt * (split + 1)) / splits);
-        t_lo = a;
-        t_hi = b;
+        const int nt = u_hi;
+        u_lo = (int)(((int64_t)nt * split) / splits);
+        u_hi = (int)(((int64_t)nt * (split + 1)) / splits);
     }
+    auto tile_of = [&](int u) { return u < n_keep ? u : t_lo + (u - n_keep); };
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
 
     // a tile's rows: eight lanes copy one cache row (128 contiguous bytes per step), sixteen rows per pass.  The page numbers of a
     // tile are looked up one tile ahead of its copies, so that the table read never stands between a warp and its next MMAs.
     const int lr = tid >> 3, lc = tid & 7;
-    auto lookup = [&](int t, int (&pg)[BN / 16]) {
+    auto lookup = [&](int u, int (&pg)[BN / 16]) {
+        const int t = tile_of(u);
 #pragma unroll
         for (int p = 0; p < BN / 16; ++p) {
             const int j = t * BN + p * 16 + lr;
-            pg[p] = (t < t_hi && j < kmax) ? bt[bs_shift >= 0 ? j >> bs_shift : j / block_size] : -1;
+            pg[p] = (u < u_hi && j < kmax) ? bt[bs_shift >= 0 ? j >> bs_shift : j / block_size] : -1;
         }
     };
-    auto load_tile = [&](int buf, int t, const int (&pg)[BN / 16]) {
-        const int j0 = t * BN;
+    auto load_tile = [&](int buf, int u, const int (&pg)[BN / 16]) {
+        const int j0 = tile_of(u) * BN;
         __nv_bfloat16* kd = Ks + buf * BN * KSTR;
         __nv_bfloat16* vd = Vs + buf * BN * VSTR;
         constexpr int KC = DK / 8, VC = DV / 8;
@@ -321,14 +342,14 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
 #pragma unroll
             for (int c = lc; c < KC; c += 8) wm_cp16(smem_u32(kd + r * KSTR + c * 8), ok ? src + g * DK + c * 8 : src, nb);
 #pragma unroll
-            for (int c = lc; c < VC; c += 8) wm_cp16(smem_u32(vd + r * VSTR + c * 8), ok ? src + v_off + g * DV + c * 8 : src, nb);
+            for (int c = lc; c < VC; c += 8) wm_cp16(smem_u32(vd + r * VSTR + c * 8), ok ? src + v_off + vh * DV + c * 8 : src, nb);
         }
         wm_commit();
     };
     int pg[BN / 16];
-    lookup(t_lo, pg);
-    if (t_lo < t_hi) load_tile(0, t_lo, pg);
-    lookup(t_lo + 1, pg);
+    lookup(u_lo, pg);
+    if (u_lo < u_hi) load_tile(0, u_lo, pg);
+    lookup(u_lo + 1, pg);
 
     // queries of this CTA's rows (plain loads; visible after the loop's first barrier)
     for (int e = tid; e < BM * (DK / 8); e += 128) {
@@ -376,18 +397,18 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
 #pragma unroll
     for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
-    for (int t = t_lo; t < t_hi; ++t) {
-        const int buf = (t - t_lo) & 1;
-        if (t + 1 < t_hi) {
-            load_tile(buf ^ 1, t + 1, pg);
-            lookup(t + 2, pg);
+    for (int u = u_lo; u < u_hi; ++u) {
+        const int buf = (u - u_lo) & 1;
+        if (u + 1 < u_hi) {
+            load_tile(buf ^ 1, u + 1, pg);
+            lookup(u + 2, pg);
             wm_wait<1>();
         } else {
             wm_wait<0>();
         }
         __syncthreads();
-        const int j0 = t * BN + wkey;                                 // first key this warp multiplies
-        if (w_hi >= j0 && w_lo < j0 + WK) {                              // warp-uniform: some row of this warp sees some key of its share
+        const int j0 = tile_of(u) * BN + wkey;                        // first key this warp multiplies
+        if (w_hi >= j0 && (w_lo < j0 + WK || j0 < keep_first)) {         // warp-uniform: some row of this warp sees some key of its share
             const __nv_bfloat16* kt = Ks + buf * BN * KSTR + wkey * KSTR;
             const __nv_bfloat16* vt = Vs + buf * BN * VSTR + wkey * VSTR;
             float sc[WK / 8][4];
@@ -436,8 +457,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int hh = e >> 1;
-                        const int dist = pos_r[hh] - (j0 + n * 8 + 2 * t4 + (e & 1));
-                        const bool ok = live[hh] && dist >= 0 && (window <= 0 || dist < window);
+                        const int jj = j0 + n * 8 + 2 * t4 + (e & 1);
+                        const int dist = pos_r[hh] - jj;
+                        const bool ok = live[hh] && dist >= 0 && (window <= 0 || dist < window || jj < keep_first);
                         const float v = ok ? fmaf(sc[n][e], scale2, -slope2[hh] * (float)dist) : -INFINITY;
                         sc[n][e] = v;
                         m_new[hh] = fmaxf(m_new[hh], v);
@@ -537,16 +559,18 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
                     a = fmaf(pr[w * WSTEP + 2 + c], f, a);
                 }
             }
-            const int i = rr / rep, h = g * rep + (rr - i * rep);
+            const int i = rr / rep, hv = (g * rep + (rr - i * rep)) * vsets + vs;
             if (splits > 1) {
-                float* pp = part + (((int64_t)s * splits + split) * H + h) * (DV + 2);
+                float* pp = part + (((int64_t)s * splits + split) * HV + hv) * (DV + 2);
                 if (c == 0) {
                     pp[0] = M;
                     pp[1] = L;
                 }
                 pp[2 + c] = a;
+            } else if (out32) {
+                out32[((int64_t)(sp.q0 + i) * HV + hv) * DV + c] = a / L;
             } else {
-                out[((int64_t)(sp.q0 + i) * H + h) * DV + c] = __float2bfloat16_rn(a / L);
+                out[((int64_t)(sp.q0 + i) * HV + hv) * DV + c] = __float2bfloat16_rn(a / L);
             }
         }
     } else {
@@ -554,9 +578,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
     for (int hh = 0; hh < 2; ++hh) {
         const int rr = row0 + warp * 16 + gq + 8 * hh;
         if (rr >= nrows) continue;
-        const int i = rr / rep, h = g * rep + (rr - i * rep);
+        const int i = rr / rep, hv = (g * rep + (rr - i * rep)) * vsets + vs;
         if (splits > 1) {                                                // decode rows only (one token per sequence): i == 0
-            float* pp = part + (((int64_t)s * splits + split) * H + h) * (DV + 2);
+            float* pp = part + (((int64_t)s * splits + split) * HV + hv) * (DV + 2);
             if (t4 == 0) {
                 pp[0] = m_run[hh];
                 pp[1] = l_run[hh];
@@ -568,10 +592,16 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
             }
         } else {
             const float inv = 1.0f / l_run[hh];
-            __nv_bfloat16* op = out + ((int64_t)(sp.q0 + i) * H + h) * DV;
+            const int64_t ob = ((int64_t)(sp.q0 + i) * HV + hv) * DV;
+            if (out32) {
 #pragma unroll
-            for (int n = 0; n < DV / 8; ++n)
-                *reinterpret_cast<uint32_t*>(op + n * 8 + 2 * t4) = wm_pack(o[n][2 * hh] * inv, o[n][2 * hh + 1] * inv);
+                for (int n = 0; n < DV / 8; ++n)
+                    *reinterpret_cast<float2*>(out32 + ob + n * 8 + 2 * t4) = make_float2(o[n][2 * hh] * inv, o[n][2 * hh + 1] * inv);
+            } else {
+#pragma unroll
+                for (int n = 0; n < DV / 8; ++n)
+                    *reinterpret_cast<uint32_t*>(out + ob + n * 8 + 2 * t4) = wm_pack(o[n][2 * hh] * inv, o[n][2 * hh + 1] * inv);
+            }
         }
     }
     }
@@ -579,7 +609,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(
 
 // out[s, h, :] = sum_k acc_k 2^(m_k - M) / sum_k l_k 2^(m_k - M) over the `splits` partials of a decode row
 __global__ void window_merge_kernel(const float* __restrict__ part, const int32_t* __restrict__ ctx_lens, __nv_bfloat16* __restrict__ out,
-                                    int H, int vdim, int splits) {
+                                    float* __restrict__ out32, int H, int vdim, int splits) {
     B200_PDL_SYNC();
     const int s = blockIdx.x, h = blockIdx.y;
     if (ctx_lens[s] <= 0) return;
@@ -596,15 +626,16 @@ __global__ void window_merge_kernel(const float* __restrict__ part, const int32_
             const float mk = base[k * step];
             if (mk != -INFINITY) a = fmaf(base[k * step + 2 + c], exp2f(mk - M), a);
         }
-        out[((int64_t)s * H + h) * vdim + c] = __float2bfloat16_rn(a * inv);
+        if (out32) out32[((int64_t)s * H + h) * vdim + c] = a * inv;
+        else out[((int64_t)s * H + h) * vdim + c] = __float2bfloat16_rn(a * inv);
     }
 }
 
 template <int DK, int DV, bool KS, bool QREG, int BN>
 int launch_window_mma_as(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
                          int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
-                         const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
-                         float* part, cudaStream_t stream) {
+                         const float* slopes, int window, int keep_first, int vsets, void* out, bool out_f32, int num_seqs, int max_q,
+                         int H, int G, float scale, int splits, float* part, cudaStream_t stream) {
     using bf = __nv_bfloat16;
     constexpr int BM = KS ? 16 : WM_BM;
     const size_t smem = sizeof(bf) * ((size_t)BM * (DK + 8) + 2 * (size_t)BN * (DK + 8) + 2 * (size_t)BN * (DV + 8));
@@ -613,28 +644,31 @@ int launch_window_mma_as(const void* q, int64_t q_stride, const void* cache, int
     int bs_shift = -1;
     if ((block_size & (block_size - 1)) == 0)
         for (bs_shift = 0; (1 << bs_shift) < block_size; ++bs_shift) {}
-    dim3 grid((max_q * (H / G) + BM - 1) / BM, num_seqs, G * splits);
+    dim3 grid((max_q * (H / G) + BM - 1) / BM, num_seqs, G * vsets * splits);
+    bf* out16 = out_f32 ? nullptr : static_cast<bf*>(out);
+    float* out32 = out_f32 ? static_cast<float*>(out) : nullptr;
     B200_LAUNCH((window_attn_mma_kernel<DK, DV, KS, QREG, BN>), grid, 128, smem, stream, static_cast<const bf*>(q), q_stride,
                 static_cast<const bf*>(cache), row_elems, v_off, block_tables, bt_stride, block_size, bs_shift, cu_q, cu_k, ctx_lens,
-                slopes, window, static_cast<bf*>(out), H, G, scale, splits, part);
+                slopes, window, keep_first, vsets, out16, out32, H, G, scale, splits, part);
     rc = b200_launch_status(nullptr);
     if (rc != B200_OK || splits <= 1) return rc;
-    B200_LAUNCH((window_merge_kernel), dim3(num_seqs, H), DV < 64 ? 32 : 64, 0, stream, part, ctx_lens, static_cast<bf*>(out), H, DV, splits);
+    B200_LAUNCH((window_merge_kernel), dim3(num_seqs, H * vsets), DV < 64 ? 32 : 64, 0, stream, part, ctx_lens, out16, out32, H * vsets, DV,
+                splits);
     return b200_launch_status(nullptr);
 }
 
 template <int DK, int DV>
 int launch_window_mma(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off, const int32_t* block_tables,
                       int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
-                      const float* slopes, int window, void* out, int num_seqs, int max_q, int H, int G, float scale, int splits,
-                      float* part, cudaStream_t stream) {
+                      const float* slopes, int window, int keep_first, int vsets, void* out, bool out_f32, int num_seqs, int max_q, int H,
+                      int G, float scale, int splits, float* part, cudaStream_t stream) {
     if (cu_q == nullptr && H / G <= 16)                   // single-token step: the four warps share every key tile
         return launch_window_mma_as<DK, DV, true, true, 64>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                                  ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
+                                                  ctx_lens, slopes, window, keep_first, vsets, out, out_f32, num_seqs, max_q, H, G, scale, splits, part, stream);
     // row-tiled form: query fragments are re-read from shared memory per key tile (measured faster than 32 more live registers)
     // (32-key tiles, which let four CTAs instead of two share an SM at 128-wide heads, were measured and are not faster)
     return launch_window_mma_as<DK, DV, false, false, 64>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                                          ctx_lens, slopes, window, out, num_seqs, max_q, H, G, scale, splits, part, stream);
+                                                          ctx_lens, slopes, window, keep_first, vsets, out, out_f32, num_seqs, max_q, H, G, scale, splits, part, stream);
 }
 
 }  // namespace
@@ -661,12 +695,14 @@ extern "C" int b200m_qk_norm_store(void* qkv, int64_t stride, int q_cols, int k_
 
 extern "C" int b200m_window_attention(const void* q, int64_t q_stride, const void* cache, int row_elems, int v_off,
                                       const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
-                                      const int32_t* cu_k, const int32_t* ctx_lens, const float* slopes, int window, void* out,
-                                      int total_q, int num_seqs, int max_q, int num_heads, int num_kv_heads, int dim, int vdim,
-                                      float scale, int is32, int flags, int splits, float* part, void* stream) {
+                                      const int32_t* cu_k, const int32_t* ctx_lens, const float* slopes, int window, int keep_first,
+                                      int all_values, void* out, int total_q, int num_seqs, int max_q, int num_heads, int num_kv_heads,
+                                      int dim, int vdim, float scale, int is32, int flags, int splits, float* part, void* stream) {
     if (!q || !cache || !block_tables || !out || total_q < 0 || num_seqs < 0 || num_heads <= 0 || num_kv_heads <= 0 ||
-        num_heads % num_kv_heads || dim <= 0 || vdim <= 0 || block_size <= 0)
+        num_heads % num_kv_heads || dim <= 0 || vdim <= 0 || block_size <= 0 || keep_first < 0)
         return B200_EINVAL;
+    const int vsets = all_values ? num_kv_heads : 1;
+    const bool out_f32 = (flags & 2) != 0 && !is32;
     if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
     if (total_q == 0 || num_seqs == 0 || max_q <= 0) return B200_OK;
     if (vdim > 512) return B200_EUNSUPPORTED;
@@ -679,8 +715,8 @@ extern "C" int b200m_window_attention(const void* q, int64_t q_stride, const voi
 #define WA_MMA(DK, DV)                                                                                                           \
     if (dim == DK && vdim == DV)                                                                                                 \
         return launch_window_mma<DK, DV>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride, block_size, cu_q, cu_k,  \
-                                         ctx_lens, slopes, window, out, num_seqs, max_q, num_heads, num_kv_heads, scale, splits, \
-                                         part, st)
+                                         ctx_lens, slopes, window, keep_first, vsets, out, out_f32, num_seqs, max_q, num_heads,  \
+                                         num_kv_heads, scale, splits, part, st)
         WA_MMA(32, 32);
         WA_MMA(32, 64);
         WA_MMA(32, 128);
@@ -694,8 +730,9 @@ extern "C" int b200m_window_attention(const void* q, int64_t q_stride, const voi
     }
 #define WA_FMA(OACC)                                                                                                             \
     B200M_DISPATCH(is32, return (launch_window_fma<T, OACC>(q, q_stride, cache, row_elems, v_off, block_tables, bt_stride,       \
-                                                            block_size, cu_q, cu_k, ctx_lens, slopes, window, out, num_seqs,     \
-                                                            max_q, num_heads, num_kv_heads, dim, vdim, scale, st)))
+                                                            block_size, cu_q, cu_k, ctx_lens, slopes, window, keep_first, vsets, \
+                                                            out, out_f32, num_seqs, max_q, num_heads, num_kv_heads, dim, vdim,   \
+                                                            scale, st)))
     const int oacc = (vdim + 31) / 32;
     if (oacc <= 1) WA_FMA(1);
     if (oacc <= 2) WA_FMA(2);
@@ -704,4 +741,123 @@ extern "C" int b200m_window_attention(const void* q, int64_t q_stride, const voi
     WA_FMA(16);
 #undef WA_FMA
     return B200_EUNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Per-head query/key norm with a partial pair rotation, unit-RMS values, and the mixing of the heads' attention weights.
+//
+//   headnorm_rope_store_kernel : per token and head, q <- rms_norm(q) * wq (one weight vector of `dim` elements shared by all
+//                                heads), the pairs (2i, 2i + 1), i < rope_dims / 2, turned by the token's position, in place;
+//                                keys the same with wk and scattered to the token's cache row; values divided by their root mean
+//                                square (no weight) and scattered next to the keys.  One warp per head, fp32 throughout, one
+//                                rounding at the store.
+//   head_mix_gate_kernel       : out[t, h, :] = c * gate(t, h, :) * sum_g mix[h, g] * acc[t, g, h / (H / G), :], where acc[t, g, v, :]
+//                                is head g's softmax weights applied to the values of value head v (window attention with
+//                                all_values): mixing the weight matrices of the heads after the softmax is linear in them, so
+//                                it commutes with the product by the values.  gate = sigmoid of a projection column.
+// ---------------------------------------------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(128) headnorm_rope_store_kernel(T* __restrict__ x, int64_t stride, int q_off, int k_off, int v_off, int H,
+                                                                  int G, int dim, int vdim, const T* __restrict__ wq,
+                                                                  const T* __restrict__ wk, int v_unit, const float* __restrict__ cos_sin,
+                                                                  int rope_dims, const int64_t* __restrict__ positions,
+                                                                  const int32_t* __restrict__ slots, T* __restrict__ cache, float eps) {
+    B200_PDL_SYNC();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    T* row = x + (int64_t)t * stride;
+    const int slot = slots ? slots[t] : -1;
+    const float* cs = cos_sin ? cos_sin + positions[t] * rope_dims : nullptr;
+    const int half = rope_dims / 2;
+    T* crow = (cache && slot >= 0) ? cache + (int64_t)slot * ((int64_t)G * (dim + vdim)) : nullptr;
+    for (int r = warp; r < H + 2 * G; r += nw) {
+        const bool is_q = r < H, is_k = !is_q && r < H + G;
+        const int d = (is_q || is_k) ? dim : vdim;
+        const T* src = is_q ? row + q_off + (int64_t)r * dim : is_k ? row + k_off + (int64_t)(r - H) * dim : row + v_off + (int64_t)(r - H - G) * vdim;
+        T* dst = is_q ? row + q_off + (int64_t)r * dim
+                      : (crow ? (is_k ? crow + (int64_t)(r - H) * dim : crow + (int64_t)G * dim + (int64_t)(r - H - G) * vdim) : nullptr);
+        if (dst == nullptr) continue;                      // keys and values of a token without a cache slot
+        const T* w = is_q ? wq : is_k ? wk : nullptr;
+        const bool normed = is_q ? wq != nullptr : is_k ? wk != nullptr : v_unit != 0;
+        float rstd = 1.0f;
+        if (normed) {
+            float ss = 0.f;
+            for (int c = lane; c < d; c += 32) {
+                const float v = ldf(src + c);
+                ss = fmaf(v, v, ss);
+            }
+            rstd = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+        }
+        const bool rot = cs != nullptr && (is_q || is_k);
+        for (int c = 2 * lane; c < d; c += 64) {           // a lane owns whole pairs
+            float a = ldf(src + c) * rstd, b = c + 1 < d ? ldf(src + c + 1) * rstd : 0.f;
+            if (w) {
+                a *= ldf(w + c);
+                if (c + 1 < d) b *= ldf(w + c + 1);
+            }
+            const int i = c >> 1;
+            if (rot && i < half) {
+                const float co = cs[i], si = cs[half + i];
+                const float ra = a * co - b * si, rb = b * co + a * si;
+                a = ra;
+                b = rb;
+            }
+            stf(dst + c, a);
+            if (c + 1 < d) stf(dst + c + 1, b);
+        }
+    }
+}
+
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) head_mix_gate_kernel(const A* __restrict__ acc, const float* __restrict__ mix, const T* __restrict__ gate,
+                                                            int64_t gate_stride, T* __restrict__ out, int64_t out_stride, float out_scale,
+                                                            int H, int G, int vdim) {
+    B200_PDL_SYNC();
+    const int64_t t = blockIdx.x;
+    const int rep = H / G;
+    const A* a = acc + t * (int64_t)H * G * vdim;
+    for (int e = threadIdx.x; e < H * vdim; e += blockDim.x) {
+        const int h = e / vdim, c = e - h * vdim, v = h / rep;
+        float sum = 0.f;
+        for (int g = 0; g < H; ++g) sum = fmaf(mix[h * H + g], ldf(a + ((int64_t)g * G + v) * vdim + c), sum);
+        const float z = gate ? sigmoidf_(ldf(gate + t * gate_stride + e)) : 1.0f;
+        stf(out + t * out_stride + e, sum * z * out_scale);
+    }
+}
+
+}  // namespace
+
+extern "C" int b200m_headnorm_rope_store(void* x, int64_t stride, int q_off, int k_off, int v_off, int num_heads, int num_kv_heads, int dim,
+                                         int vdim, const void* q_norm_w, const void* k_norm_w, int v_unit_norm, const float* cos_sin,
+                                         int rope_dims, const int64_t* positions, const int32_t* slots, void* cache, int n, float eps,
+                                         int is32, void* stream) {
+    if (!x || n < 0 || num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 || rope_dims < 0 || rope_dims > dim || (rope_dims & 1))
+        return B200_EINVAL;
+    if ((cos_sin && rope_dims > 0 && !positions) || (cache && !slots)) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    if (rope_dims == 0) cos_sin = nullptr;
+    B200M_DISPATCH(is32, B200_LAUNCH((headnorm_rope_store_kernel<T>), n, 128, 0, static_cast<cudaStream_t>(stream), static_cast<T*>(x), stride,
+                                     q_off, k_off, v_off, num_heads, num_kv_heads, dim, vdim, static_cast<const T*>(q_norm_w),
+                                     static_cast<const T*>(k_norm_w), v_unit_norm, cos_sin, rope_dims, positions, slots,
+                                     static_cast<T*>(cache), eps));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_head_mix_gate(const void* acc, int acc_f32, const float* mix, const void* gate, int64_t gate_stride, void* out,
+                                   int64_t out_stride, float out_scale, int n, int num_heads, int num_kv_heads, int vdim, int is32,
+                                   void* stream) {
+    if (!acc || !mix || !out || n < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || vdim <= 0) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (is32 || acc_f32) {
+        B200M_DISPATCH(is32, B200_LAUNCH((head_mix_gate_kernel<T, float>), n, 256, 0, st, static_cast<const float*>(acc), mix,
+                                         static_cast<const T*>(gate), gate_stride, static_cast<T*>(out), out_stride, out_scale, num_heads,
+                                         num_kv_heads, vdim));
+    } else {
+        using bf = __nv_bfloat16;
+        B200_LAUNCH((head_mix_gate_kernel<bf, bf>), n, 256, 0, st, static_cast<const bf*>(acc), mix, static_cast<const bf*>(gate),
+                    gate_stride, static_cast<bf*>(out), out_stride, out_scale, num_heads, num_kv_heads, vdim);
+    }
+    return b200_launch_status(nullptr);
 }

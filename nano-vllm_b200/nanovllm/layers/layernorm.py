@@ -49,3 +49,24 @@ class SublayerOutputNorm:
     def __call__(self, x, y, mult: float, copy=None) -> None:
         from .. import mixops
         mixops.add_normed(x, y, self.weight, mult, self.eps, w_offset=1.0, copy=copy)
+
+
+class SandwichNorm:
+    """The norms around one sublayer of a block that norms a sublayer on both sides, ``x <- x + norm_out(f(norm_in(x)))``, both RMS norms
+    with weights stored around zero (``x / sqrt(mean(x^2) + eps) * (1 + w)``) over an fp32 stream.  ``open`` norms the stream
+    for the sublayer; ``close`` norms the sublayer's output, updates the stream and, given the sublayer that follows, opens
+    that one in the same pass (``copy``: the updated rows in the activation type instead, for a consumer that reads the stream itself)."""
+
+    def __init__(self, width: int, eps: float, dtype, device):
+        self.eps = eps
+        self.w_in = torch.zeros(width, dtype=dtype, device=device)
+        self.w_out = torch.zeros(width, dtype=dtype, device=device)
+
+    def open(self, x):
+        from .. import mixops
+        return mixops.rmsnorm_rows(x, self.w_in, self.eps, w_offset=1.0)
+
+    def close(self, x, y, then: "SandwichNorm | None" = None, copy=None):
+        from .. import mixops
+        return mixops.add_normed_norm(x, y, self.w_out, self.eps, w_offset=1.0, next_weight=then.w_in if then is not None else None,
+                                      next_offset=1.0, copy=copy)

@@ -1,6 +1,7 @@
 """Feed-forward blocks of hybrid decoders: a gated dense block and a routed mixture of small experts.
 
 Dense:   W_down (gelu_tanh(W_gate h) * (W_up h))
+Biased:  W_down gelu_tanh(W_up h + b_up) + b_down
 Routed:  z = W_router h (fp32), s = sigmoid(z); the `top` experts with the largest s get weight s (not renormalised);
          the weight scales the expert's INPUT:  out = sum_e expert_e(s_e h),  expert(x) = W_down relu(W_up x)^2;
          an optional shared expert of the same form runs for every token, scaled by sigmoid(W_sg h).
@@ -43,6 +44,30 @@ class GatedDenseFF:
     def forward(self, h: torch.Tensor):
         """-> (T tensor, None)"""
         return F.linear(mixops.ff_act(F.linear(h, self.w_gate_up), mixops.FF_GELU_TANH_MUL), self.w_down), None
+
+
+class BiasedDenseFF:
+    """W_down act(W_up h + b_up) + b_down with the tanh form of GELU: an ungated dense block whose projections carry biases
+    (added in the GEMM epilogues)."""
+
+    def __init__(self, width: int, mlp: dict, dtype, device):
+        self.ff = int(mlp["ff"])
+        e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        self.w_up, self.b_up = e(self.ff, width), e(self.ff)
+        self.w_down, self.b_down = e(width, self.ff), e(width)
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        named = {"up": self.w_up, "up.b": self.b_up, "down": self.w_down, "down.b": self.b_down}
+        if leaf not in named:
+            return False
+        named[leaf].copy_(w)
+        return True
+
+    def weight_shapes(self, width: int) -> dict:
+        return {"up": (self.ff, width), "up.b": (self.ff,), "down": (width, self.ff), "down.b": (width,)}
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return F.linear(mixops.ff_act(F.linear(h, self.w_up, self.b_up), mixops.FF_GELU_TANH), self.w_down, self.b_down)
 
 
 class RoutedExpertsFF:

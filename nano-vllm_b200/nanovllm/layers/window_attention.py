@@ -85,3 +85,120 @@ class BiasedWindowAttention:
         o = mixops.window_attention(qkv, self.cache, ctx.block_tables, self.block_size, spans, self.heads, self.kv_heads, self.dim,
                                     self.vdim, self.scale, self.slopes, self.window)
         return F.linear(o, self.w_o)
+
+
+class MixedHeadWindowAttention:
+    """Grouped-query attention with per-head query/key norms, a partial pair rotation, unit-RMS values, a sliding window that
+    keeps a sequence's first tokens, head mixing after the softmax and a sigmoid output gate.
+
+        q = W_q h + b_q,  k = W_k h + b_k,  v = W_v h + b_v
+        q[h] <- rotate(rms(q[h]) * g_q),  k[g] <- rotate(rms(k[g]) * g_k)     (g_q, g_k: `dim` weights shared by the heads; rotation of the
+                                                                                first rot.dims elements, pair (2i, 2i+1) by p * base^(-2i / dims))
+        v[g] <- v[g] / rms(v[g])                                                (no weight; cached so)
+        s[h, i, j] = (q_i[h] . k_j[h // (H / G)]) * scale,   visible j:  j <= i and (i - j < window or j < keep_first)
+        p[h] = softmax over the visible j;   p'[h] = sum_g T[h, g] p[g];   o[h] = sum_j p'[h]_ij v_j[h // (H / G)]
+        out = W_o (concat_h o[h] * sigmoid(W_g h))
+
+    Keys are cached after norm and rotation, values after their norm: one row ``[k (G * dim) | v (G * vdim)]`` per token, pass and
+    layer.  The head mixing is linear in the weight matrices, so it commutes with the product by the values: the attention
+    kernel applies every head's weights to the values of every value head (one online-softmax pass, fp32 results), and a
+    row-wise kernel forms ``sum_g T[h, g] (p[g] V[h // (H / G)])`` and the gate.
+
+    The input projection ``[W_q ; W_k ; W_v ; W_g]``, its bias and the output projection may be views into the merged weights
+    of a block that runs this mixer beside another one on the same input (``ParallelMixer``).
+    """
+    kind = "mixed_head_attention"
+
+    def __init__(self, width: int, m: dict, eps: float, dtype, device, max_position: int, w_in=None, b_in=None, w_o=None):
+        from .rotary_embedding import build_interleaved_cos_sin
+        self.width, self.eps, self.dtype, self.device = width, eps, dtype, device
+        self.heads, self.kv_heads = int(m["heads"]), int(m["kv_heads"])
+        self.dim, self.vdim = int(m["dim"]), int(m["vdim"])
+        self.scale = float(m["scale"])
+        mask = m.get("mask") or {}
+        self.window = int(mask.get("size") or 0)                  # 0: every earlier token is visible
+        self.keep_first = int(mask.get("keep_first") or 0) if self.window else 0
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        if self.vdim > 512:
+            raise ValueError(f"vdim {self.vdim}: the attention kernels hold at most 512 output columns per query row")
+        H, G, d, vd = self.heads, self.kv_heads, self.dim, self.vdim
+        self.q_cols, self.k_cols, self.v_cols = H * d, G * d, G * vd
+        self.in_cols, self.out_cols = self.q_cols + self.k_cols + self.v_cols + H * vd, H * vd
+        rot = m.get("rot")
+        self.cos_sin, self.rot_key = None, None
+        if rot and int(rot["dims"]) > 0:
+            dims = int(rot["dims"])
+            if dims > d or dims % 2:
+                raise ValueError("rot.dims must be even and at most dim")
+            self.rot_key = (dims, float(rot["base"]), max_position)
+            self.cos_sin = build_interleaved_cos_sin(dims, max_position, float(rot["base"]), None, device)
+        e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        self.w_in = w_in if w_in is not None else e(self.in_cols, width)          # [W_q ; W_k ; W_v ; W_g]: one GEMM reads h once
+        self.b_in = b_in if b_in is not None else torch.zeros(self.in_cols, dtype=dtype, device=device)
+        self.w_o = w_o if w_o is not None else e(width, self.out_cols)
+        assert self.w_in.shape == (self.in_cols, width) and self.b_in.shape == (self.in_cols,) and self.w_o.shape == (width, self.out_cols)
+        self.q_norm, self.k_norm = e(d), e(d)
+        self.talk = torch.zeros(H, H, dtype=torch.float32, device=device)
+        self.cache: list = []                             # per pass [num_blocks * block_size, G * (dim + vdim)]
+        self.block_size = 0
+
+    @staticmethod
+    def projection_cols(m: dict) -> tuple[int, int]:
+        """(rows of the wide input projection, columns of the output projection) for a mixer configuration."""
+        H, G, d, vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        return H * d + G * d + G * vd + H * vd, H * vd
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        q, k, v = self.q_cols, self.k_cols, self.v_cols
+        spans = {"q": (0, q), "k": (q, q + k), "v": (q + k, q + k + v), "g": (q + k + v, self.in_cols)}
+        if leaf in spans:
+            self.w_in[spans[leaf][0]:spans[leaf][1]].copy_(w)
+        elif leaf in ("q.b", "k.b", "v.b"):
+            a, b = spans[leaf[0]]
+            self.b_in[a:b].copy_(w)
+        elif leaf == "q.norm":
+            self.q_norm.copy_(w)
+        elif leaf == "k.norm":
+            self.k_norm.copy_(w)
+        elif leaf == "talk":
+            self.talk.copy_(w.float())
+        elif leaf == "o":
+            self.w_o.copy_(w)
+        else:
+            return False
+        return True
+
+    def weight_shapes(self, width: int) -> dict:
+        H = self.heads
+        return {"q": (self.q_cols, width), "q.b": (self.q_cols,), "k": (self.k_cols, width), "k.b": (self.k_cols,), "v": (self.v_cols, width),
+                "v.b": (self.v_cols,), "q.norm": (self.dim,), "k.norm": (self.dim,), "talk": (H, H), "g": (H * self.vdim, width),
+                "o": (width, H * self.vdim)}
+
+    def cache_row_elems(self) -> int:
+        return self.k_cols + self.v_cols
+
+    def state_slot_bytes(self) -> int:
+        return 0
+
+    def bind(self, num_blocks: int, block_size: int, num_slots: int, copies: int = 1) -> None:
+        self.block_size = block_size
+        self.cache = [torch.zeros(num_blocks * block_size, self.cache_row_elems(), dtype=self.dtype, device=self.device) for _ in range(copies)]
+
+    def unbind(self) -> None:
+        self.cache = []
+
+    def mix(self, proj: torch.Tensor, h: torch.Tensor, positions, ctx, spans: mixops.StepSpans, inst: int, out: torch.Tensor | None = None,
+            out_scale: float = 1.0) -> torch.Tensor:
+        """proj [n, in_cols] = h W_in^T + b_in (a row-strided view) -> the output projection's operand [n, heads * vdim]."""
+        q, k, v = self.q_cols, self.k_cols, self.v_cols
+        cache = self.cache[inst]
+        mixops.headnorm_rope_store(proj, 0, q, q + k, self.heads, self.kv_heads, self.dim, self.vdim, self.q_norm, self.k_norm, True,
+                                   self.cos_sin, positions, ctx.slot_mapping, cache, self.eps)
+        acc = mixops.window_attention(proj, cache, ctx.block_tables, self.block_size, spans, self.heads, self.kv_heads, self.dim, self.vdim,
+                                      self.scale, None, self.window, keep_first=self.keep_first, all_values=True,
+                                      out_f32=self.dtype != torch.float32)
+        return mixops.head_mix_gate(acc, self.talk, proj[:, q + k + v:], self.dtype, out=out, out_scale=out_scale)
+
+    def forward(self, h: torch.Tensor, positions, ctx, spans: mixops.StepSpans, inst: int = 0) -> torch.Tensor:
+        return F.linear(self.mix(F.linear(h, self.w_in, self.b_in), h, positions, ctx, spans, inst), self.w_o)

@@ -77,6 +77,44 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def embed_pair(ids: torch.Tensor, table: torch.Tensor, scale: float, spans: "StepSpans", pair: torch.Tensor | None = None,
+               buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0, prev_tok: torch.Tensor | None = None,
+               state_slots: torch.Tensor | None = None, copy: torch.Tensor | None = None) -> torch.Tensor:
+    """ids int64 [n] -> fp32 [n, width] = table[id] * scale + pair[(prev * mul_prev + id * mul_cur) % buckets]; the first token
+    of a sequence takes row ``buckets`` of ``pair``.  ``prev_tok`` (int64 [slots]) supplies the token before a portion and is
+    left holding the portion's last token."""
+    assert ids.dtype == torch.int64 and ids.is_contiguous() and table.is_contiguous()
+    n, width = ids.numel(), table.shape[1]
+    is32 = _is32(table)
+    out = torch.empty(n, width, dtype=torch.float32, device=table.device)
+    if pair is not None:
+        _same(is32, pair)
+        assert pair.is_contiguous() and pair.shape == (buckets + 1, width) and prev_tok.dtype == torch.int64
+        assert state_slots.dtype == torch.int32 and state_slots.numel() >= spans.num_seqs
+        ops.LAUNCHES[0] += 1
+    assert copy is None or (copy.dtype == table.dtype and copy.is_contiguous() and copy.shape == out.shape)
+    _call("b200m_embed_pair", ids.data_ptr(), table.data_ptr(), scale, _p(pair), buckets, mul_prev, mul_cur, _p(prev_tok),
+          _p(state_slots), _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), _p(copy), spans.num_seqs, spans.max_q,
+          width, table.shape[0], is32, _stream())
+    return out
+
+
+def add_normed_norm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, w_offset: float = 0.0, mult: float = 1.0,
+                    next_weight: torch.Tensor | None = None, next_offset: float = 0.0, copy: torch.Tensor | None = None):
+    """``add_normed``, then the RMS norm of the updated rows with ``next_weight`` (the next sublayer's input), returned in the
+    weight's dtype (None without ``next_weight``)."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2 and y.is_contiguous() and y.shape == x.shape
+    is32 = _is32(weight)
+    y32 = y.dtype == torch.float32 and not is32
+    if not y32:
+        _same(is32, y)
+    _same(is32, next_weight, copy)
+    out = torch.empty(x.shape, dtype=weight.dtype, device=x.device) if next_weight is not None else None
+    _call("b200m_add_normed_norm", x.data_ptr(), None if y32 else y.data_ptr(), y.data_ptr() if y32 else None, weight.data_ptr(), mult,
+          w_offset, _p(copy), _p(next_weight), next_offset, _p(out), x.shape[0], x.shape[1], eps, is32, _stream())
+    return out
+
+
 def add_normed(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, mult: float, eps: float, w_offset: float = 0.0,
                copy: torch.Tensor | None = None) -> None:
     """x (fp32 [rows, cols], in place) += mult * rms_norm(y) * (w_offset + weight): the norm sits on the sublayer's output.
@@ -138,12 +176,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, cols: int | None 
     return out
 
 
-FF_GELU_TANH_MUL, FF_RELU2, FF_SILU_MUL = 0, 1, 2
+FF_GELU_TANH_MUL, FF_RELU2, FF_SILU_MUL, FF_GELU_TANH = 0, 1, 2, 3
 
 
 def ff_act(x: torch.Tensor, kind: int, out: torch.Tensor | None = None) -> torch.Tensor:
     assert x.dim() == 2 and x.is_contiguous()
-    n = x.shape[1] if kind == FF_RELU2 else x.shape[1] // 2
+    n = x.shape[1] if kind in (FF_RELU2, FF_GELU_TANH) else x.shape[1] // 2
     if out is None:
         out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
     _call("b200m_ff_act", x.data_ptr(), out.data_ptr(), x.shape[0], n, kind, _is32(x), _stream())
@@ -207,37 +245,131 @@ def qk_norm_store(qkv: torch.Tensor, q_cols: int, k_cols: int, v_cols: int, q_no
 
 def window_attention(q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor, block_size: int, spans: StepSpans,
                      heads: int, kv_heads: int, dim: int, vdim: int, scale: float, slopes: torch.Tensor | None = None,
-                     window: int = 0, fma: bool = False, splits: int | None = None) -> torch.Tensor:
-    """q [n, >= heads * dim] (row-strided view), cache [slots, kv_heads * (dim + vdim)] -> [n, heads * vdim]."""
+                     window: int = 0, fma: bool = False, splits: int | None = None, keep_first: int = 0, all_values: bool = False,
+                     out_f32: bool = False) -> torch.Tensor:
+    """q [n, >= heads * dim] (row-strided view), cache [slots, kv_heads * (dim + vdim)] -> [n, heads * vdim].
+    ``keep_first``: the first tokens of a sequence that stay visible beyond the window.  ``all_values``: every head's weights
+    meet the values of every value head, -> [n, heads, kv_heads, vdim] (``head_mix_gate`` mixes them).  ``out_f32``: fp32 result."""
     n = q.shape[0]
     assert q.dim() == 2 and q.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == kv_heads * (dim + vdim)
     assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1
     assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == heads)
     is32 = _is32(q)
     _same(is32, cache)
-    out = torch.empty(n, heads * vdim, dtype=q.dtype, device=q.device)
+    vsets = kv_heads if all_values else 1
+    out = torch.empty(n, heads * vsets * vdim, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     part, nsplit = None, 1
     if splits is None:
-        splits = window_attention_splits(spans, block_tables.shape[1] * block_size, window, kv_heads) if (not is32 and not fma) else 1
+        splits = window_attention_splits(spans, block_tables.shape[1] * block_size, window, kv_heads * vsets, keep_first) \
+            if (not is32 and not fma) else 1
     if splits > 1 and spans.cu_q is None and not is32 and not fma:
         nsplit = splits
-        part = torch.empty(spans.num_seqs * nsplit * heads * (vdim + 2), dtype=torch.float32, device=q.device)
+        part = torch.empty(spans.num_seqs * nsplit * heads * vsets * (vdim + 2), dtype=torch.float32, device=q.device)
         ops.LAUNCHES[0] += 1
     _call("b200m_window_attention", q.data_ptr(), q.stride(0), cache.data_ptr(), cache.shape[-1], kv_heads * dim,
           block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
-          _p(slopes), int(window), out.data_ptr(), n, spans.num_seqs, spans.max_q, heads, kv_heads, dim, vdim, scale, is32,
-          int(fma), nsplit, _p(part), _stream())
-    return out
+          _p(slopes), int(window), int(keep_first), int(all_values), out.data_ptr(), n, spans.num_seqs, spans.max_q, heads, kv_heads,
+          dim, vdim, scale, is32, int(fma) | (2 if out_f32 else 0), nsplit, _p(part), _stream())
+    return out.view(n, heads, vsets, vdim) if all_values else out
 
 
-def window_attention_splits(spans: StepSpans, max_keys: int, window: int, kv_heads: int) -> int:
+def window_attention_splits(spans: StepSpans, max_keys: int, window: int, kv_heads: int, keep_first: int = 0) -> int:
     """How many CTAs share the visible keys of one decode row: enough for about two CTAs per SM, at least two 64-key tiles each.
     Static per (batch rows, table width), so the choice also holds inside a captured graph."""
     if spans.cu_q is not None:
         return 1
-    keys = min(max_keys, window) if window > 0 else max_keys
+    keys = min(max_keys, window + keep_first) if window > 0 else max_keys
     tiles = -(-keys // 64)
     return max(1, min(tiles // 2, 32, (2 * _sm_count()) // max(spans.num_seqs * kv_heads, 1)))
+
+
+def headnorm_rope_store(x: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                        q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, v_unit_norm: bool, cos_sin: torch.Tensor | None,
+                        positions: torch.Tensor | None, slots: torch.Tensor | None, cache: torch.Tensor | None, eps: float) -> None:
+    """x [n, cols] (q heads at q_off, key heads at k_off, value heads at v_off): per-head RMS norm of q and k with one weight of
+    ``dim`` elements shared by the heads, pair rotation by cos_sin [positions, rope_dims] (fp32), q in place; normed, rotated keys
+    and (unit-RMS) values into cache rows [k (kv_heads * dim) | v (kv_heads * vdim)] at ``slots``."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    is32 = _is32(x)
+    _same(is32, q_norm, k_norm, cache)
+    rope_dims = 0
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and positions.dtype == torch.int64
+        rope_dims = cos_sin.shape[1]
+    if cache is not None:
+        assert cache.is_contiguous() and cache.shape[-1] == kv_heads * (dim + vdim) and slots.dtype == torch.int32 and slots.numel() == x.shape[0]
+    _call("b200m_headnorm_rope_store", x.data_ptr(), x.stride(0), q_off, k_off, v_off, heads, kv_heads, dim, vdim, _p(q_norm), _p(k_norm),
+          int(v_unit_norm), _p(cos_sin), rope_dims, _p(positions), _p(slots), _p(cache), x.shape[0], eps, is32, _stream())
+
+
+def head_mix_gate(acc: torch.Tensor, mix: torch.Tensor, gate: torch.Tensor | None, dtype, out: torch.Tensor | None = None,
+                  out_scale: float = 1.0) -> torch.Tensor:
+    """acc [n, H, G, vdim] (head g's weights on value head v), mix fp32 [H, H], gate [n, H * vdim] (row-strided view) ->
+    [n, H * vdim] = out_scale * sigmoid(gate) * sum_g mix[h, g] acc[:, g, h // (H / G)]; ``out`` may be a row-strided view."""
+    n, H, G, vdim = acc.shape
+    assert acc.is_contiguous() and mix.dtype == torch.float32 and mix.is_contiguous() and mix.shape == (H, H)
+    assert gate is None or (gate.stride(1) == 1 and gate.shape == (n, H * vdim) and gate.dtype == dtype)
+    if out is None:
+        out = torch.empty(n, H * vdim, dtype=dtype, device=acc.device)
+    assert out.dtype == dtype and out.shape == (n, H * vdim) and out.stride(1) == 1
+    _call("b200m_head_mix_gate", acc.data_ptr(), int(acc.dtype == torch.float32), mix.data_ptr(), _p(gate), gate.stride(0) if gate is not None else 0,
+          out.data_ptr(), out.stride(0), out_scale, n, H, G, vdim, int(dtype == torch.float32), _stream())
+    return out
+
+
+# ---- gated diagonal recurrence and gated delta rule ------------------------------------------------------------------------
+def diag_scan(u: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, rate: torch.Tensor, y: torch.Tensor, state: torch.Tensor,
+              state_slots: torch.Tensor, spans: StepSpans, chunk: int = 64) -> torch.Tensor:
+    """u [n, C]; gates fp32 [C / cb, n, 2 cb] (per block: pre-activations of r, then of i); gate_bias fp32 [C / cb, 2 cb];
+    rate fp32 [C] (<= 0); y [n, C] (row-strided view); state fp32 [slots, C] -> S * gelu_tanh(y), [n, C]."""
+    n, C = u.shape
+    nb, rows, cb2 = gates.shape
+    assert u.stride(1) == 1 and y.stride(1) == 1 and gates.dtype == torch.float32 and gates.is_contiguous() and rows == n and nb * cb2 == 2 * C
+    assert gate_bias.dtype == torch.float32 and gate_bias.is_contiguous() and gate_bias.numel() == 2 * C
+    assert rate.dtype == torch.float32 and rate.numel() == C and state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == C
+    is32 = _is32(u)
+    _same(is32, y)
+    out = torch.empty(n, C, dtype=u.dtype, device=u.device)
+    ws = None
+    if spans.max_q > 2 * chunk:            # long portions: chunks in parallel (three launches) instead of one serial walk
+        ws = torch.empty(spans.num_seqs * (-(-spans.max_q // chunk)) * C * 2, dtype=torch.float32, device=u.device)
+        ops.LAUNCHES[0] += 2
+    _call("b200m_diag_scan", u.data_ptr(), u.stride(0), gates.data_ptr(), n, gate_bias.data_ptr(), rate.data_ptr(), y.data_ptr(), y.stride(0),
+          state.data_ptr(), state_slots.data_ptr(), _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs,
+          spans.max_q, C, cb2 // 2, chunk, _p(ws), is32, _stream())
+    return out
+
+
+def gated_delta(x: torch.Tensor, q_off: int, k_off: int, v_off: int, ba: torch.Tensor, rate: torch.Tensor, dt_bias: torch.Tensor,
+                state: torch.Tensor, state_slots: torch.Tensor, spans: StepSpans, heads: int, kv_heads: int, dim: int, vdim: int,
+                q_scale: float) -> torch.Tensor:
+    """x [n, cols]: convolved q, k ([kv_heads, dim] at q_off / k_off) and v ([heads, vdim] at v_off); ba fp32 [n, 2 heads];
+    state fp32 [slots, heads, vdim, dim] -> fp32 [n, heads, vdim]."""
+    n = x.shape[0]
+    assert x.dim() == 2 and x.stride(1) == 1 and ba.dtype == torch.float32 and ba.stride(1) == 1 and ba.shape == (n, 2 * heads)
+    assert rate.dtype == torch.float32 and dt_bias.dtype == torch.float32 and rate.numel() == heads and dt_bias.numel() == heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, vdim, dim)
+    out = torch.empty(n, heads, vdim, dtype=torch.float32, device=x.device)
+    _call("b200m_gated_delta", x.data_ptr(), x.stride(0), q_off, k_off, v_off, ba.data_ptr(), ba.stride(0), rate.data_ptr(), dt_bias.data_ptr(),
+          state.data_ptr(), state_slots.data_ptr(), _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, heads,
+          kv_heads, dim, vdim, q_scale, _is32(x), _stream())
+    return out
+
+
+def head_rmsnorm_gate(x: torch.Tensor, weight: torch.Tensor | None, gate: torch.Tensor | None, eps: float, dtype, silu: bool = True,
+                      out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    """x fp32 [n, H, vdim] -> [n, H * vdim] = out_scale * x / rms(x) * weight * act(gate), per head; act = silu or sigmoid;
+    ``out`` may be a row-strided view."""
+    n, H, vdim = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    assert gate is None or (gate.stride(1) == 1 and gate.shape == (n, H * vdim) and gate.dtype == dtype)
+    assert weight is None or (weight.dtype == dtype and weight.numel() == vdim)
+    if out is None:
+        out = torch.empty(n, H * vdim, dtype=dtype, device=x.device)
+    assert out.dtype == dtype and out.shape == (n, H * vdim) and out.stride(1) == 1
+    _call("b200m_head_rmsnorm_gate", x.data_ptr(), _p(weight), _p(gate), gate.stride(0) if gate is not None else 0, int(silu), out.data_ptr(),
+          out.stride(0), out_scale, n, H, vdim, eps, int(dtype == torch.float32), _stream())
+    return out
 
 
 # ---- selective scan ------------------------------------------------------------------------------------------------------
@@ -245,8 +377,8 @@ SCAN_CHUNK = 64          # tokens per chunk of the chunk-parallel form
 
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
-                state_slots: torch.Tensor, spans: StepSpans, out: torch.Tensor | None = None) -> torch.Tensor:
-    """x [n, channels] (row-strided view) -> silu(conv(x) + bias) [n, channels]; conv_state [slots, taps - 1, channels] fp32
+                state_slots: torch.Tensor, spans: StepSpans, out: torch.Tensor | None = None, silu: bool = True) -> torch.Tensor:
+    """x [n, channels] (row-strided view) -> silu(conv(x) + bias) [n, channels] (``silu=False``: no activation); conv_state [slots, taps - 1, channels] fp32
     is read for the history and left holding the inputs that follow."""
     channels, taps = weight.shape
     assert x.dim() == 2 and x.stride(1) == 1 and x.shape[1] == channels and weight.is_contiguous()
@@ -256,8 +388,8 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     if out is None:
         out = torch.empty(x.shape[0], channels, dtype=x.dtype, device=x.device)
     _call("b200m_causal_conv", x.data_ptr(), x.stride(0), weight.data_ptr(), _p(bias), conv_state.data_ptr(), state_slots.data_ptr(),
-          _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, spans.max_q, channels, taps, is32,
-          _stream())
+          _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens), out.data_ptr(), spans.num_seqs, spans.max_q, channels, taps, int(silu),
+          is32, _stream())
     if taps > 1:
         ops.LAUNCHES[0] += 1
     return out

@@ -33,8 +33,18 @@ def _tipetar_config(raw: dict):
     return TipetarConfig(raw)
 
 
-MODELS = {"Qwen3ForCausalLM": _qwen3, "Qwen2ForCausalLM": _qwen3, "Tafopel": _tafopel, "Tipetar": _tipetar}
-CONFIG_READERS = {"Tafopel": _tafopel_config, "Tipetar": _tipetar_config}
+def _musavik():
+    from .musavik import MusavikForCausalLM
+    return MusavikForCausalLM
+
+
+def _musavik_config(raw: dict):
+    from .musavik import MusavikConfig
+    return MusavikConfig(raw)
+
+
+MODELS = {"Qwen3ForCausalLM": _qwen3, "Qwen2ForCausalLM": _qwen3, "Tafopel": _tafopel, "Tipetar": _tipetar, "Musavik": _musavik}
+CONFIG_READERS = {"Tafopel": _tafopel_config, "Tipetar": _tipetar_config, "Musavik": _musavik_config}
 
 
 def architecture_of(hf_config) -> str:
