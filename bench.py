@@ -545,11 +545,21 @@ def main():
                     help="instead of the headline workload: prefill / decode throughput of the Tipetar decoder (windowed attention, group-routed "
                          "experts) beside Tafopel and Qwen3 at equal size, with a per-kernel roofline table (profiles/window_bench.py); one GPU")
     ap.add_argument("--windowed-sizes", default="w1024,w2048")
+    ap.add_argument("--recurrent", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the Musavik decoder (gated diagonal recurrence, windowed "
+                         "attention with mixed heads beside a gated delta rule, repeated layers) beside Tafopel, Tipetar and Qwen3 at equal size, with a "
+                         "per-kernel roofline table (profiles/recurrent_bench.py); one GPU")
+    ap.add_argument("--recurrent-sizes", default="w1024,w2048")
     args = ap.parse_args()
     if args.windowed:
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
         import window_bench
         window_bench.main(["--sizes", args.windowed_sizes])
+        return
+    if args.recurrent:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
+        import recurrent_bench
+        recurrent_bench.main(["--sizes", args.recurrent_sizes])
         return
     if args.hybrid:
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))

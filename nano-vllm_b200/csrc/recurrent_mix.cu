@@ -20,8 +20,7 @@
 //     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //   Columns of S are independent, so a thread group of four lanes owns one column (dim / 4 state elements per lane in
 //   registers) and walks the tokens; a CTA covers 32 columns of one (sequence, head).  The decay folds into the update:
-//   d = S_old^T k;  u = beta (v - g d);  S_new = g S_old + k u.  The next token's operands are fetched while the current one is
-//   worked on.
+//   d = S_old^T k;  u = beta (v - g d);  S_new = g S_old + k u.  Tokens are staged through shared memory a chunk ahead.
 #include "mix_common.cuh"
 
 namespace {
@@ -109,7 +108,12 @@ __global__ void __launch_bounds__(128) diag_carry_kernel(float* __restrict__ ws,
 constexpr int GD_LANES = 4;            // lanes that share one column of the state
 constexpr int GD_COLS = 32;            // columns per CTA (128 threads)
 
-// DPL state rows per lane: row d = k * GD_LANES + sub, k < DPL.  state: [slots, H, vdim, dim] (a column's rows are contiguous).
+// DPL state rows per lane: lane `sub` of a column's group owns rows sub * DPL .. sub * DPL + DPL - 1 (zero beyond dim).
+// state: [slots, H, vdim, dim] (a column's rows are contiguous).
+// Tokens are staged through shared memory TB at a time, as fp32: the chunk after the current one is fetched into registers
+// before the current one is worked on and stored afterwards (two buffers), so the serial walk never waits for global memory.
+// A staged key or query row is four lane segments of DPL floats, each padded by four: 128-bit reads without bank conflicts.
+// After a chunk lands, 128 / TB threads per token form its unit-norm factors, write strength and decay once for the CTA.
 template <typename T, int DPL>
 __global__ void __launch_bounds__(GD_LANES * GD_COLS) gated_delta_kernel(
     const T* __restrict__ x, int64_t stride, int q_off, int k_off, int v_off,     // per token: q, k [G, dim], v [H, vdim] (convolved, activated)
@@ -119,79 +123,159 @@ __global__ void __launch_bounds__(GD_LANES * GD_COLS) gated_delta_kernel(
     const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens, float* __restrict__ out,      // [n, H, vdim] fp32
     int H, int G, int dim, int vdim, float q_scale) {
     B200_PDL_SYNC();
-    const int h = blockIdx.x, s = blockIdx.y;
+    constexpr int NT = GD_LANES * GD_COLS;
+    constexpr int TB = DPL >= 64 ? 8 : 16;
+    constexpr int SEG = DPL + 4, ROW = GD_LANES * SEG, DP = GD_LANES * DPL;
+    constexpr int PF = (TB * DP) / NT;                     // key (and query) elements a thread fetches per chunk
+    constexpr int PV = (TB * GD_COLS) / NT;                // value elements a thread fetches per chunk
+    constexpr int TPT = NT / TB;                           // threads that share one token's factors
+    __shared__ __align__(16) float ks[2][TB][ROW];
+    __shared__ __align__(16) float qs[2][TB][ROW];
+    __shared__ float vs[2][TB][GD_COLS];
+    __shared__ float sc[2][TB][4];                         // key normaliser, query normaliser * scale, write strength, decay
+    const int h = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
     const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
     if (sp.qlen <= 0) return;
-    const int sub = threadIdx.x % GD_LANES;
-    const int col = blockIdx.z * GD_COLS + threadIdx.x / GD_LANES;
+    const int sub = tid % GD_LANES;
+    const int col0 = blockIdx.z * GD_COLS, col = col0 + tid / GD_LANES;
     const bool live = col < vdim;
     const int cc = live ? col : vdim - 1;
     const int g = h / (H / G);
-    float* st = state + (((int64_t)state_slots[s] * H + h) * vdim + cc) * dim;
+    float* st = state + (((int64_t)state_slots[s] * H + h) * vdim + cc) * dim + sub * DPL;
     const bool has_hist = sp.klen - sp.qlen > 0;
+    const bool vec_state = dim == GD_LANES * DPL;           // whole lane segments (then 16-byte aligned too): 128-bit state accesses
     float S[DPL];
+    if (has_hist && vec_state) {
 #pragma unroll
-    for (int k = 0; k < DPL; ++k) {
-        const int d = k * GD_LANES + sub;
-        S[k] = (has_hist && d < dim) ? st[d] : 0.f;
+        for (int k = 0; k < DPL / 4; ++k) {
+            const float4 f = reinterpret_cast<const float4*>(st)[k];
+            S[4 * k] = f.x, S[4 * k + 1] = f.y, S[4 * k + 2] = f.z, S[4 * k + 3] = f.w;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) S[k] = (has_hist && sub * DPL + k < dim) ? st[k] : 0.f;
     }
     const float rt = rate[h], db = dt_bias[h];
     const T* qp = x + q_off + (int64_t)g * dim;
     const T* kp = x + k_off + (int64_t)g * dim;
-    const T* vp = x + v_off + (int64_t)h * vdim + cc;
-    float kn[DPL], qn[DPL], vn, bn, an;                      // the next token's operands
-    auto fetch = [&](int i) {
-        const int64_t row = sp.q0 + i;
+    const T* vp = x + v_off + (int64_t)h * vdim + col0;
+    float fk[PF], fq[PF], fv[PV], fb = 0.f, fa = 0.f;      // the next chunk, in flight
+    auto fetch = [&](int i0) {
 #pragma unroll
-        for (int k = 0; k < DPL; ++k) {
-            const int d = k * GD_LANES + sub;
-            kn[k] = d < dim ? ldf(kp + row * stride + d) : 0.f;
-            qn[k] = d < dim ? ldf(qp + row * stride + d) : 0.f;
+        for (int j = 0; j < PF; ++j) {
+            const int e = tid + NT * j, t = e / DP, d = e - t * DP;
+            const bool ok = i0 + t < sp.qlen && d < dim;
+            const int64_t row = sp.q0 + i0 + t;
+            fk[j] = ok ? ldf(kp + row * stride + d) : 0.f;
+            fq[j] = ok ? ldf(qp + row * stride + d) : 0.f;
         }
-        vn = ldf(vp + row * stride);
-        bn = ba[row * ba_stride + h];
-        an = ba[row * ba_stride + H + h];
+#pragma unroll
+        for (int j = 0; j < PV; ++j) {
+            const int e = tid + NT * j, t = e / GD_COLS, c = e - t * GD_COLS;
+            fv[j] = (i0 + t < sp.qlen && col0 + c < vdim) ? ldf(vp + (int64_t)(sp.q0 + i0 + t) * stride + c) : 0.f;
+        }
+        if (tid < TB && i0 + tid < sp.qlen) {
+            fb = ba[(int64_t)(sp.q0 + i0 + tid) * ba_stride + h];
+            fa = ba[(int64_t)(sp.q0 + i0 + tid) * ba_stride + H + h];
+        }
     };
-    fetch(0);
-    for (int i = 0; i < sp.qlen; ++i) {
-        float kk[DPL], qq[DPL];
-        float ssk = 0.f, ssq = 0.f;
+    auto land = [&](int buf) {                             // registers -> shared memory
 #pragma unroll
-        for (int k = 0; k < DPL; ++k) {
-            kk[k] = kn[k];
-            qq[k] = qn[k];
-            ssk = fmaf(kk[k], kk[k], ssk);
-            ssq = fmaf(qq[k], qq[k], ssq);
+        for (int j = 0; j < PF; ++j) {
+            const int e = tid + NT * j, t = e / DP, d = e - t * DP;
+            const int at = (d / DPL) * SEG + (d % DPL);
+            ks[buf][t][at] = fk[j];
+            qs[buf][t][at] = fq[j];
         }
-        const float v = vn, beta = sigmoidf_(bn), gdec = expf(rt * softplus_(an + db));
-        if (i + 1 < sp.qlen) fetch(i + 1);
-        float dk = 0.f;
 #pragma unroll
-        for (int k = 0; k < DPL; ++k) dk = fmaf(S[k], kk[k], dk);
+        for (int j = 0; j < PV; ++j) {
+            const int e = tid + NT * j;
+            vs[buf][e / GD_COLS][e % GD_COLS] = fv[j];
+        }
+        if (tid < TB) {
+            sc[buf][tid][2] = sigmoidf_(fb);
+            sc[buf][tid][3] = expf(rt * softplus_(fa + db));
+        }
+    };
+    auto factors = [&](int buf) {                          // after a barrier: the unit-norm factors of the chunk's tokens
+        const int t = tid / TPT, j = tid % TPT;
+        float ssk = 0.f, ssq = 0.f;
+        for (int d = j; d < DP; d += TPT) {
+            const int at = (d / DPL) * SEG + (d % DPL);
+            const float a = ks[buf][t][at], b = qs[buf][t][at];
+            ssk = fmaf(a, a, ssk);
+            ssq = fmaf(b, b, ssq);
+        }
 #pragma unroll
-        for (int o = 1; o < GD_LANES; o <<= 1) {
+        for (int o = 1; o < TPT; o <<= 1) {
             ssk += __shfl_xor_sync(0xffffffffu, ssk, o);
             ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-            dk += __shfl_xor_sync(0xffffffffu, dk, o);
         }
-        const float rk = 1.0f / sqrtf(ssk + 1e-6f), rq = q_scale / sqrtf(ssq + 1e-6f);
-        const float uw = beta * (v - gdec * dk * rk) * rk;   // u times the key's normaliser: S += (k rk) u
-        float oq = 0.f;
-#pragma unroll
-        for (int k = 0; k < DPL; ++k) {
-            S[k] = fmaf(kk[k], uw, gdec * S[k]);
-            oq = fmaf(S[k], qq[k], oq);
+        if (j == 0) {
+            sc[buf][t][0] = 1.0f / sqrtf(ssk + 1e-6f);
+            sc[buf][t][1] = q_scale / sqrtf(ssq + 1e-6f);
         }
+    };
+    fetch(0);
+    land(0);
+    __syncthreads();
+    factors(0);
+    __syncthreads();
+    for (int i0 = 0, buf = 0; i0 < sp.qlen; i0 += TB, buf ^= 1) {
+        const bool more = i0 + TB < sp.qlen;
+        if (more) fetch(i0 + TB);
+        const int nt = min(TB, sp.qlen - i0);
+        for (int t = 0; t < nt; ++t) {
+            const float4* kr = reinterpret_cast<const float4*>(&ks[buf][t][sub * SEG]);
+            const float4* qr = reinterpret_cast<const float4*>(&qs[buf][t][sub * SEG]);
+            float4 kk[DPL / 4];
+            float d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int o = 1; o < GD_LANES; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-        if (live && sub == 0) out[((int64_t)(sp.q0 + i) * H + h) * vdim + col] = oq * rq;
+            for (int k = 0; k < DPL / 4; ++k) {
+                kk[k] = kr[k];
+                d4[0] = fmaf(S[4 * k], kk[k].x, d4[0]);
+                d4[1] = fmaf(S[4 * k + 1], kk[k].y, d4[1]);
+                d4[2] = fmaf(S[4 * k + 2], kk[k].z, d4[2]);
+                d4[3] = fmaf(S[4 * k + 3], kk[k].w, d4[3]);
+            }
+            float dk = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+#pragma unroll
+            for (int o = 1; o < GD_LANES; o <<= 1) dk += __shfl_xor_sync(0xffffffffu, dk, o);
+            const float rk = sc[buf][t][0], rq = sc[buf][t][1], beta = sc[buf][t][2], gdec = sc[buf][t][3];
+            const float v = vs[buf][t][tid / GD_LANES];
+            const float uw = beta * (v - gdec * dk * rk) * rk;   // u times the key's normaliser: S += (k rk) u
+            float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < DPL / 4; ++k) {
+                const float4 qq = qr[k];
+                S[4 * k] = fmaf(kk[k].x, uw, gdec * S[4 * k]);
+                S[4 * k + 1] = fmaf(kk[k].y, uw, gdec * S[4 * k + 1]);
+                S[4 * k + 2] = fmaf(kk[k].z, uw, gdec * S[4 * k + 2]);
+                S[4 * k + 3] = fmaf(kk[k].w, uw, gdec * S[4 * k + 3]);
+                o4[0] = fmaf(S[4 * k], qq.x, o4[0]);
+                o4[1] = fmaf(S[4 * k + 1], qq.y, o4[1]);
+                o4[2] = fmaf(S[4 * k + 2], qq.z, o4[2]);
+                o4[3] = fmaf(S[4 * k + 3], qq.w, o4[3]);
+            }
+            float oq = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+#pragma unroll
+            for (int o = 1; o < GD_LANES; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
+            if (live && sub == 0) out[((int64_t)(sp.q0 + i0 + t) * H + h) * vdim + col] = oq * rq;
+        }
+        if (more) {
+            land(buf ^ 1);                                 // its last readers passed the barrier that closed the previous chunk
+            __syncthreads();
+            factors(buf ^ 1);
+            __syncthreads();
+        }
     }
-    if (live) {
+    if (live && vec_state) {
 #pragma unroll
-        for (int k = 0; k < DPL; ++k) {
-            const int d = k * GD_LANES + sub;
-            if (d < dim) st[d] = S[k];
-        }
+        for (int k = 0; k < DPL / 4; ++k) reinterpret_cast<float4*>(st)[k] = make_float4(S[4 * k], S[4 * k + 1], S[4 * k + 2], S[4 * k + 3]);
+    } else if (live) {
+#pragma unroll
+        for (int k = 0; k < DPL; ++k)
+            if (sub * DPL + k < dim) st[k] = S[k];
     }
 }
 

@@ -809,20 +809,58 @@ __global__ void __launch_bounds__(128) headnorm_rope_store_kernel(T* __restrict_
     }
 }
 
-template <typename T, typename A>
+// One thread per (value head v, VEC columns) of a token: it reads head g's accumulator for that value head once and feeds the
+// H / G output heads that own value head v (eight at a time), so every accumulator element is read once.  The mixing matrix
+// sits in shared memory.  VEC = 4 (fp32 accumulators, vdim a multiple of four): 128-bit accumulator reads.
+template <typename T, typename A, int VEC>
 __global__ void __launch_bounds__(256) head_mix_gate_kernel(const A* __restrict__ acc, const float* __restrict__ mix, const T* __restrict__ gate,
                                                             int64_t gate_stride, T* __restrict__ out, int64_t out_stride, float out_scale,
                                                             int H, int G, int vdim) {
     B200_PDL_SYNC();
+    constexpr int RB = 8;
+    extern __shared__ float hm_mix[];                      // [H][H]
+    for (int e = threadIdx.x; e < H * H; e += blockDim.x) hm_mix[e] = mix[e];
+    __syncthreads();
     const int64_t t = blockIdx.x;
-    const int rep = H / G;
+    const int rep = H / G, vq = vdim / VEC;
     const A* a = acc + t * (int64_t)H * G * vdim;
-    for (int e = threadIdx.x; e < H * vdim; e += blockDim.x) {
-        const int h = e / vdim, c = e - h * vdim, v = h / rep;
-        float sum = 0.f;
-        for (int g = 0; g < H; ++g) sum = fmaf(mix[h * H + g], ldf(a + ((int64_t)g * G + v) * vdim + c), sum);
-        const float z = gate ? sigmoidf_(ldf(gate + t * gate_stride + e)) : 1.0f;
-        stf(out + t * out_stride + e, sum * z * out_scale);
+    for (int e = threadIdx.x; e < G * vq; e += blockDim.x) {
+        const int v = e / vq, c = (e - v * vq) * VEC;
+        for (int r0 = 0; r0 < rep; r0 += RB) {
+            float sum[RB][VEC];
+#pragma unroll
+            for (int r = 0; r < RB; ++r)
+#pragma unroll
+                for (int x = 0; x < VEC; ++x) sum[r][x] = 0.f;
+            const float* m = hm_mix + (v * rep + r0) * H;
+            for (int g = 0; g < H; ++g) {
+                float xv[VEC];
+                const A* src = a + ((int64_t)g * G + v) * vdim + c;
+                if constexpr (VEC == 4) {
+                    const float4 f = *reinterpret_cast<const float4*>(src);
+                    xv[0] = f.x, xv[1] = f.y, xv[2] = f.z, xv[3] = f.w;
+                } else {
+                    xv[0] = ldf(src);
+                }
+#pragma unroll
+                for (int r = 0; r < RB; ++r)
+                    if (r0 + r < rep) {
+                        const float w = m[r * H + g];
+#pragma unroll
+                        for (int x = 0; x < VEC; ++x) sum[r][x] = fmaf(w, xv[x], sum[r][x]);
+                    }
+            }
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                if (r0 + r >= rep) break;
+                const int o = (v * rep + r0 + r) * vdim + c;
+#pragma unroll
+                for (int x = 0; x < VEC; ++x) {
+                    const float z = gate ? sigmoidf_(ldf(gate + t * gate_stride + o + x)) : 1.0f;
+                    stf(out + t * out_stride + o + x, sum[r][x] * z * out_scale);
+                }
+            }
+        }
     }
 }
 
@@ -850,13 +888,20 @@ extern "C" int b200m_head_mix_gate(const void* acc, int acc_f32, const float* mi
     if (!acc || !mix || !out || n < 0 || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || vdim <= 0) return B200_EINVAL;
     if (n == 0) return B200_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (is32 || acc_f32) {
-        B200M_DISPATCH(is32, B200_LAUNCH((head_mix_gate_kernel<T, float>), n, 256, 0, st, static_cast<const float*>(acc), mix,
+    const size_t smem = sizeof(float) * (size_t)num_heads * num_heads;
+    if (smem > 48 * 1024) return B200_EUNSUPPORTED;
+    const bool vec = (is32 || acc_f32) && vdim % 4 == 0 && reinterpret_cast<uintptr_t>(acc) % 16 == 0;
+    if (vec) {
+        B200M_DISPATCH(is32, B200_LAUNCH((head_mix_gate_kernel<T, float, 4>), n, 256, smem, st, static_cast<const float*>(acc), mix,
+                                         static_cast<const T*>(gate), gate_stride, static_cast<T*>(out), out_stride, out_scale, num_heads,
+                                         num_kv_heads, vdim));
+    } else if (is32 || acc_f32) {
+        B200M_DISPATCH(is32, B200_LAUNCH((head_mix_gate_kernel<T, float, 1>), n, 256, smem, st, static_cast<const float*>(acc), mix,
                                          static_cast<const T*>(gate), gate_stride, static_cast<T*>(out), out_stride, out_scale, num_heads,
                                          num_kv_heads, vdim));
     } else {
         using bf = __nv_bfloat16;
-        B200_LAUNCH((head_mix_gate_kernel<bf, bf>), n, 256, 0, st, static_cast<const bf*>(acc), mix, static_cast<const bf*>(gate),
+        B200_LAUNCH((head_mix_gate_kernel<bf, bf, 1>), n, 256, smem, st, static_cast<const bf*>(acc), mix, static_cast<const bf*>(gate),
                     gate_stride, static_cast<bf*>(out), out_stride, out_scale, num_heads, num_kv_heads, vdim);
     }
     return b200_launch_status(nullptr);
