@@ -32,12 +32,12 @@ def musavik_config(size: str):
     rec = {"type": "rglru", "mixer": {"width": width, "blocks": blocks, "conv": 4}}
     par = {"type": "parallel", "mixer": {
         "left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window, "keep_first": keep},
-                 "rot": {"dims": 64, "base": 1e6}},
+                 "rot": {"dims": 64, "base": 5e5}},
         "right": {"heads": dh, "kv_heads": dg, "dim": 128, "vdim": 128, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}}
     mlp = {"kind": "dense", "ff": 3 * width}
     layers = [dict(l, mlp=mlp) for l in (rec, par, rec, par, rec, par)]
     return MusavikConfig({"architecture": "Musavik", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6},
-                          "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+                          "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 40503, "mul_cur": 9973}},
                           "layers": layers, "loop": {"start": 2, "stop": 4, "times": 2}})
 
 
@@ -95,7 +95,7 @@ def kernel_table(size: str, peaks: dict):
     add("head_mix_gate 8192 rows", lambda: mixops.head_mix_gate(acc, T, gate, bf), n * H * d * (G * 4 + 2 + 2), n * H * H * d * 2, "fma")
     # ---- per-head norms, rotation and cache store; Tipetar's whole-projection norm + store beside it ----
     from nanovllm.layers.rotary_embedding import build_interleaved_cos_sin
-    table = build_interleaved_cos_sin(64, 8192, 1e6, None, dev)
+    table = build_interleaved_cos_sin(64, 8192, 5e5, None, dev)
     qkv = rn(n, (H + 2 * G) * d)
     cache = torch.zeros(n, G * 2 * d, dtype=bf, device=dev)
     sl = torch.arange(n, dtype=torch.int32, device=dev)
@@ -143,7 +143,7 @@ def kernel_table(size: str, peaks: dict):
     ids = torch.randint(0, VOCAB, (n,), device=dev)
     tab, pair = rn(VOCAB, width), rn(65522, width)
     prev, sl4 = torch.zeros(4, dtype=torch.int64, device=dev), torch.arange(4, dtype=torch.int32, device=dev)
-    add("embed_pair 8192 rows", lambda: mixops.embed_pair(ids, tab, 3.0, spans(4, 2048, 2048), pair, 65521, 31, 17, prev, sl4), n * width * (2 + 2 + 4), 0)
+    add("embed_pair 8192 rows", lambda: mixops.embed_pair(ids, tab, 3.0, spans(4, 2048, 2048), pair, 65521, 40503, 9973, prev, sl4), n * width * (2 + 2 + 4), 0)
     add("tafopel embed 8192 rows", lambda: mixops.embed(ids, tab), n * width * (2 + 4), 0)
     return rows
 
