@@ -75,26 +75,46 @@ int b200m_rmsnorm(const void* x, int64_t x_stride, const void* w, void* out, int
  * 3: out = gelu_tanh(x) (n per row). */
 int b200m_ff_act(const void* x, void* out, int64_t rows, int n, int kind, int is32, void* stream);
 
+/* Gated unit with clamped branches: x = [gate | up] (2n of x_stride elements per row), g = min(gate, limit), u = clamp(up, -limit, limit),
+ * out = g * sigmoid(alpha * g) * (u + 1). */
+int b200m_ff_glu_clamped(const void* x, int64_t x_stride, void* out, int64_t rows, int n, float limit, float alpha, int is32, void* stream);
+
+/* One sublayer's close in a layer that gates and norms the sublayer's result and scales it per column:
+ *   t = y * sigmoid(gate)  (gate NULL: t = y);   x += t / sqrt(mean(t^2) + eps) * w_out;
+ *   out_next (optional) = x / sqrt(mean(x^2) + eps) * next_scale * w_next   (w_next NULL: 1).
+ * x fp32 [rows, cols] in place; y in the activation type (or y32, fp32), contiguous; gate in the activation type with row stride
+ * gate_stride (a column slice of a wider projection); w_out, w_next fp32 [cols]; out_next in the activation type. */
+int b200m_gated_add_normed_norm(float* x, const void* y, const float* y32, const void* gate, int64_t gate_stride,
+                                const float* w_out, const float* w_next, float next_scale, void* out_next, int rows, int cols,
+                                float eps, int is32, void* stream);
+
+/* x <- cap * tanh(x / cap), fp32, in place (n elements). */
+int b200m_softcap(float* x, int64_t n, float cap, void* stream);
+
 /* ---- latent attention ---------------------------------------------------------------------------------------------- */
 
 /* Per token: cache[slot] = [ rms_norm(dkv[:rank]) * norm_w | rotate(dkv[rank : rank + rot_dim]) ].  The rotation turns the
  * pairs (2i, 2i+1), i < rope_dims / 2, by cos_sin[position] = [cos (rope_dims/2) | sin (rope_dims/2)] (fp32, any magnitude
- * factor folded in); elements past rope_dims pass unchanged.  slot < 0 skips the token. */
+ * factor folded in); elements past rope_dims pass unchanged.  layout 1: the pairs are (i, i + rope_dims / 2) instead.
+ * slot < 0 skips the token. */
 int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, const float* cos_sin, int rope_dims,
                        const int64_t* positions, const int32_t* slots, void* cache, int n, int rank, int rot_dim, float eps,
-                       int is32, void* stream);
+                       int layout, int is32, void* stream);
 
-/* Multi-query attention of every head over the cached rows, causal, with a per-head sink logit in the softmax denominator.
- * q_lat [H, total_q, rank]: queries already mapped into the latent space; q_raw [total_q, H, q_head_stride]: the raw query
- * projection, whose rot_dim elements from q_rot_off on are rotated here by the token's position.  out [H, total_q, rank].
+/* Multi-query attention of every head over the cached rows, causal, with a per-head sink logit in the softmax denominator
+ * (sink NULL: an ordinary softmax).  window > 0: position i sees the keys j with 0 <= i - j < window only.  layout: the pairing of
+ * the rotated query part, as for b200m_latent_store.
+ * q_lat [H, total_q, rank]: queries already mapped into the latent space; q_raw: the raw query projection (token t, head h at
+ * t * q_tok_stride + h * q_head_stride), whose rot_dim elements from q_rot_off on are rotated here by the token's position.  out [H, total_q, rank].
  * bf16 runs on the tensor cores (mma.sync over staged key tiles); fp32, or flags & 1, on the fp32 FMA pipe.
  * splits > 1 (bf16 decode steps only, ignored elsewhere): the keys of every sequence are shared out over `splits` CTAs whose
  * partial results, fp32 [num_seqs, 4 * splits, num_heads, rank + 2] in `part`, a second launch merges. */
-int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+int b200m_latent_attention(const void* q_lat, const void* q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off, const void* cache,
                            const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
                            const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
                            int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
-                           int rot_dim, float scale, int is32, int flags, int splits, float* part, void* stream);
+                           int rot_dim, float scale, int window, int layout, int is32, int flags, int splits, float* part,
+                           void* stream);
 
 /* ---- windowed grouped-query attention ------------------------------------------------------------------------------ */
 
@@ -108,11 +128,21 @@ int b200m_qk_norm_store(void* qkv, int64_t stride, int q_cols, int k_cols, int v
  * q_norm_w with ONE weight vector of `dim` elements for all heads (NULL: no norm), then the pairs (2i, 2i+1), i < rope_dims / 2,
  * turned by cos_sin[position] = [cos (rope_dims/2) | sin (rope_dims/2)] (fp32; NULL: no rotation), in place; keys the same with
  * k_norm_w into cache[slot] = [k (G * dim) | v (G * vdim)]; values divided by their root mean square per head (v_unit_norm) or
- * copied.  cache NULL or slot < 0: queries only. */
+ * copied; v_cos_sin (optional, fp32 [positions, v_rope_dims]): the value pairs (2m, 2m+1), m < v_rope_dims / 2, are turned by the
+ * token's position before the store.  cache NULL or slot < 0: queries only. */
 int b200m_headnorm_rope_store(void* x, int64_t stride, int q_off, int k_off, int v_off, int num_heads, int num_kv_heads, int dim,
                               int vdim, const void* q_norm_w, const void* k_norm_w, int v_unit_norm, const float* cos_sin,
-                              int rope_dims, const int64_t* positions, const int32_t* slots, void* cache, int n, float eps, int is32,
-                              void* stream);
+                              int rope_dims, const float* v_cos_sin, int v_rope_dims, const int64_t* positions, const int32_t* slots,
+                              void* cache, int n, float eps, int is32, void* stream);
+
+/* out[t, h, :] = rotate(acc[t, h, :], sign * position[t]) * sigmoid(gate[t, h, :]): per-head attention results turned (back) by
+ * the query's position and gated.  acc element (t, h, c) at t * acc_tok_stride + h * acc_head_stride + c (fp32 when acc_f32, else
+ * the activation type); cos_sin fp32 [positions, rope_dims] = [cos | sin] (NULL: no rotation), pairs (2m, 2m+1) for layout 0,
+ * (m, m + rope_dims / 2) for layout 1, elements past rope_dims unchanged; gate (optional) with row stride gate_stride; out
+ * [n, num_heads * vdim] in the activation type with row stride out_stride. */
+int b200m_head_rotate_gate(const void* acc, int acc_f32, int64_t acc_tok_stride, int64_t acc_head_stride, const float* cos_sin,
+                           int rope_dims, int layout, float sign, const int64_t* positions, const void* gate, int64_t gate_stride,
+                           void* out, int64_t out_stride, int n, int num_heads, int vdim, int is32, void* stream);
 
 /* out[t, h, :] = out_scale * sigmoid(gate[t, h, :]) * sum_g mix[h, g] * acc[t, g, h / (H / G), :]: the heads' attention weights mixed after
  * the softmax, for acc [n, H, G, vdim] from b200m_window_attention with all_values (fp32 when acc_f32, else the activation

@@ -4,7 +4,9 @@
 // key/value up-projections folded into the query and the output (q_lat[h] = W_uk[h]^T q_nope[h]; head output =
 // W_uv[h] * sum_j p_j c_j) attention is multi-query over those rows:
 //     s_j = (q_lat[h] . c_j + q_rot[h] . k_rot_j) * scale,   p = softmax over {s_j, j <= pos} and a per-head sink logit
-// The sink takes part in the maximum and the denominator only: it is a key with a fixed score and a zero value.
+// The sink takes part in the maximum and the denominator only: it is a key with a fixed score and a zero value; without one
+// (sink == NULL) the softmax is the ordinary one.  window > 0 hides the keys with pos - j >= window; key tiles wholly below
+// every row's window are never staged.  The rotated parts pair (2i, 2i+1) (layout 0) or (i, i + rope_dims/2) (layout 1).
 //
 //   latent_store_kernel : RMS norm of the latent, rotation of the shared key part, scatter to the token's cache slot
 //   latent_attn_kernel  : any mix of prompt portions and single tokens (one warp per (token, head), key tiles shared
@@ -22,12 +24,15 @@ __device__ __forceinline__ void rotate_pair(float u, float v, float c, float s, 
     ou = u * c - v * s;
     ov = v * c + u * s;
 }
+// elements of pair i: (2i, 2i+1) in the interleaved layout, (i, i + half) in the halves layout
+__device__ __forceinline__ int pair_lo(int i, int half, int layout) { return layout ? i : 2 * i; }
+__device__ __forceinline__ int pair_hi(int i, int half, int layout) { return layout ? i + half : 2 * i + 1; }
 
 template <typename T>
 __global__ void __launch_bounds__(128) latent_store_kernel(const T* __restrict__ dkv, int64_t stride, const T* __restrict__ w,
                                                            const float* __restrict__ cos_sin, int rope_dims,
                                                            const int64_t* __restrict__ positions, const int32_t* __restrict__ slots,
-                                                           T* __restrict__ cache, int rank, int rot_dim, float eps) {
+                                                           T* __restrict__ cache, int rank, int rot_dim, float eps, int layout) {
     B200_PDL_SYNC();
     __shared__ float red[4];
     const int t = blockIdx.x;
@@ -46,9 +51,10 @@ __global__ void __launch_bounds__(128) latent_store_kernel(const T* __restrict__
     const int half = rope_dims / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float a, b;
-        rotate_pair(ldf(x + rank + 2 * i), ldf(x + rank + 2 * i + 1), cs[i], cs[half + i], a, b);
-        stf(dst + rank + 2 * i, a);
-        stf(dst + rank + 2 * i + 1, b);
+        const int e0 = rank + pair_lo(i, half, layout), e1 = rank + pair_hi(i, half, layout);
+        rotate_pair(ldf(x + e0), ldf(x + e1), cs[i], cs[half + i], a, b);
+        stf(dst + e0, a);
+        stf(dst + e1, b);
     }
     for (int c = rope_dims + threadIdx.x; c < rot_dim; c += blockDim.x) stf(dst + rank + c, ldf(x + rank + c));
 }
@@ -56,14 +62,15 @@ __global__ void __launch_bounds__(128) latent_store_kernel(const T* __restrict__
 // q for one (token, head) into shared memory: [q_lat (rank) | rotated q_rot (rot_dim)], fp32, pre-multiplied by scale
 template <typename T>
 __device__ __forceinline__ void load_query(float* qs, const T* q_lat, const T* q_rot, const float* cs, int rank, int rot_dim,
-                                           int rope_dims, float scale, int lane) {
+                                           int rope_dims, float scale, int lane, int layout) {
     for (int c = lane; c < rank; c += 32) qs[c] = ldf(q_lat + c) * scale;
     const int half = rope_dims / 2;
     for (int i = lane; i < half; i += 32) {
         float a, b;
-        rotate_pair(ldf(q_rot + 2 * i), ldf(q_rot + 2 * i + 1), cs[i], cs[half + i], a, b);
-        qs[rank + 2 * i] = a * scale;
-        qs[rank + 2 * i + 1] = b * scale;
+        const int e0 = pair_lo(i, half, layout), e1 = pair_hi(i, half, layout);
+        rotate_pair(ldf(q_rot + e0), ldf(q_rot + e1), cs[i], cs[half + i], a, b);
+        qs[rank + e0] = a * scale;
+        qs[rank + e1] = b * scale;
     }
     for (int c = rope_dims + lane; c < rot_dim; c += 32) qs[rank + c] = ldf(q_rot + c) * scale;
 }
@@ -72,15 +79,15 @@ __device__ __forceinline__ void load_query(float* qs, const T* q_lat, const T* q
 template <typename T, int OACC>
 __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(
     const T* __restrict__ q_lat,        // [H, total_q, rank]
-    const T* __restrict__ q_raw,        // [total_q, H, q_head_stride]; the rotated part starts at q_rot_off of each head
-    int q_head_stride, int q_rot_off,
+    const T* __restrict__ q_raw,        // token t, head h at t * q_tok_stride + h * q_head_stride; the rotated part starts at q_rot_off of each head
+    int64_t q_tok_stride, int q_head_stride, int q_rot_off,
     const T* __restrict__ cache,        // [slots, rank + rot_dim]
     const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
     const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
     const float* __restrict__ sink,     // [H]
     const float* __restrict__ cos_sin, int rope_dims,
     T* __restrict__ out,                // [H, total_q, rank]
-    int total_q, int H, int rank, int rot_dim, float scale) {
+    int total_q, int H, int rank, int rot_dim, float scale, int window, int layout) {
     B200_PDL_SYNC();
     extern __shared__ float smem[];
     const int D = rank + rot_dim;
@@ -103,15 +110,17 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(
     float* myq = qs + warp * D;
     if (active) {
         const int64_t row = sp.q0 + i;
-        load_query(myq, q_lat + ((int64_t)h * total_q + row) * rank, q_raw + (row * H + h) * q_head_stride + q_rot_off,
-                   cos_sin + (int64_t)pos * rope_dims, rank, rot_dim, rope_dims, scale, lane);
+        load_query(myq, q_lat + ((int64_t)h * total_q + row) * rank, q_raw + row * q_tok_stride + (int64_t)h * q_head_stride + q_rot_off,
+                   cos_sin + (int64_t)pos * rope_dims, rank, rot_dim, rope_dims, scale, lane, layout);
     }
-    float m = active ? sink[h] : 0.f, l = 1.0f;            // the sink: score sink[h], weight exp(0) = 1, no value
+    float m = (active && sink) ? sink[h] : -1e30f, l = sink ? 1.0f : 0.f;      // the sink: score sink[h], weight exp(0) = 1, no value
     float acc[OACC];
 #pragma unroll
     for (int k = 0; k < OACC; ++k) acc[k] = 0.f;
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
-    for (int j0 = 0; j0 < kmax; j0 += LA_TILE) {
+    // the first tile any row of this CTA sees: the lowest row's window start
+    const int j_first = window > 0 ? (max(first + pair0 / H - window + 1, 0) / LA_TILE) * LA_TILE : 0;
+    for (int j0 = j_first; j0 < kmax; j0 += LA_TILE) {
         __syncthreads();                                   // previous tile consumed (and the queries written)
         const int rows = min(LA_TILE, kmax - j0);
         for (int e = threadIdx.x; e < rows * D; e += blockDim.x) {
@@ -121,8 +130,8 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(
             tile[r * DS + c] = ldf(cache + slot * D + c);
         }
         __syncthreads();
-        if (active && j0 <= pos) {
-            const bool valid = lane < rows && j0 + lane <= pos;
+        if (active && j0 <= pos && (window <= 0 || j0 + LA_TILE > pos - window + 1)) {
+            const bool valid = lane < rows && j0 + lane <= pos && (window <= 0 || pos - (j0 + lane) < window);
             float sc = -INFINITY;
             if (valid) {
                 const float* kr = tile + lane * DS;
@@ -150,7 +159,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attn_kernel(
         }
     }
     if (active) {
-        const float inv = 1.0f / l;
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
         T* o = out + ((int64_t)h * total_q + sp.q0 + i) * rank;
 #pragma unroll
         for (int k = 0; k < OACC; ++k) {
@@ -173,19 +182,19 @@ int ensure_smem(K kernel, size_t bytes) {
 }
 
 template <typename T, int OACC>
-int launch_attn(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+int launch_attn(const void* q_lat, const void* q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off, const void* cache,
                 const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
                 const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
-                int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, cudaStream_t stream) {
+                int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int window, int layout, cudaStream_t stream) {
     const int D = rank + rot_dim;
     const size_t smem = sizeof(float) * ((size_t)LA_TILE * (D | 1) + (size_t)LA_WARPS * D + LA_WARPS * LA_TILE);
     int rc = ensure_smem(latent_attn_kernel<T, OACC>, smem);
     if (rc != B200_OK) return rc;
     dim3 grid((max_q * H + LA_WARPS - 1) / LA_WARPS, num_seqs);
     B200_LAUNCH((latent_attn_kernel<T, OACC>), grid, LA_WARPS * 32, smem, stream, static_cast<const T*>(q_lat),
-                static_cast<const T*>(q_raw), q_head_stride, q_rot_off, static_cast<const T*>(cache), block_tables, bt_stride,
+                static_cast<const T*>(q_raw), q_tok_stride, q_head_stride, q_rot_off, static_cast<const T*>(cache), block_tables, bt_stride,
                 block_size, cu_q, cu_k, ctx_lens, sink, cos_sin, rope_dims, static_cast<T*>(out), total_q, H, rank, rot_dim,
-                scale);
+                scale, window, layout);
     return b200_launch_status(nullptr);
 }
 
@@ -220,11 +229,11 @@ __host__ __device__ inline int mma_row_stride(int D) {
 // BN: keys per staged tile (64; 32 for wide rows, so that two CTAs still fit in an SM's shared memory).
 template <int NT_O, bool WS, int BN>
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
-    const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_raw, int q_head_stride, int q_rot_off,
+    const __nv_bfloat16* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off,
     const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables, int bt_stride, int block_size,
     const int32_t* __restrict__ cu_q, const int32_t* __restrict__ cu_k, const int32_t* __restrict__ ctx_lens,
     const float* __restrict__ sink, const float* __restrict__ cos_sin, int rope_dims, __nv_bfloat16* __restrict__ out,
-    int total_q, int H, int rank, int rot_dim, float scale, int splits, float* __restrict__ part) {
+    int total_q, int H, int rank, int rot_dim, float scale, int window, int layout, int splits, float* __restrict__ part) {
     B200_PDL_SYNC();
     constexpr int MMA_BN = BN;
     static_assert(!WS || BN == 64, "the warp-split form shares out 64-key tiles");
@@ -254,7 +263,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         const int i = live_row ? rr / H : 0, h = live_row ? rr - i * H : 0;
         const int64_t tok = sp.q0 + i;
         const __nv_bfloat16* ql = q_lat + ((int64_t)h * total_q + tok) * rank;
-        const __nv_bfloat16* qr = q_raw + (tok * H + h) * q_head_stride + q_rot_off;
+        const __nv_bfloat16* qr = q_raw + tok * q_tok_stride + (int64_t)h * q_head_stride + q_rot_off;
         const float* cs = cos_sin + (int64_t)(first + i) * rope_dims;
         const int half = rope_dims >> 1;
         for (int c = lane; c < DS; c += 32) {
@@ -265,9 +274,10 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
                 } else {
                     const int cr = c - rank;
                     if (cr < rope_dims) {
-                        const int p = cr >> 1;
-                        const float u = __bfloat162float(qr[2 * p]), w = __bfloat162float(qr[2 * p + 1]);
-                        v = __float2bfloat16_rn((cr & 1) ? (w * cs[p] + u * cs[half + p]) : (u * cs[p] - w * cs[half + p]));
+                        const int p = layout ? (cr < half ? cr : cr - half) : cr >> 1;
+                        const bool second = layout ? cr >= half : (cr & 1);
+                        const float u = __bfloat162float(qr[pair_lo(p, half, layout)]), w = __bfloat162float(qr[pair_hi(p, half, layout)]);
+                        v = __float2bfloat16_rn(second ? (w * cs[p] + u * cs[half + p]) : (u * cs[p] - w * cs[half + p]));
                     } else {
                         v = qr[cr];
                     }
@@ -290,8 +300,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         const bool live = rr < nrows;
         const int i = live ? rr / H : 0;
         pos_row[k] = live ? first + i : -1;
-        m_run[k] = live ? sink[rr - i * H] : 0.f;
-        l_run[k] = 1.0f;
+        m_run[k] = live ? (sink ? sink[rr - i * H] : -1e30f) : 0.f;
+        l_run[k] = (sink || !live) ? 1.0f : 0.f;
         if (split > 0 || (WS && warp > 0)) {              // the sink is counted once, by the first partial
             m_run[k] = -1e30f;
             l_run[k] = 0.f;
@@ -310,11 +320,14 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
     const int32_t* bt = block_tables + (int64_t)s * bt_stride;
     const uint32_t qs_base = smem_u32(Qs), ks_base = smem_u32(Ks);
     const bool vec = (D & 7) == 0;
-    int j_begin = 0, j_end = kmax;
+    // with a window the walk starts at the tile that holds the first key the CTA's lowest row sees
+    const int t_lo = window > 0 ? max(first + row0 / H - window + 1, 0) / MMA_BN : 0;
+    const int warp_pos_lo = first + (row0 + rwarp * 16) / H;      // smallest position among this warp's rows
+    int j_begin = t_lo * MMA_BN, j_end = kmax;
     if (splits > 1) {
-        const int tiles = (kmax + MMA_BN - 1) / MMA_BN, per = (tiles + splits - 1) / splits;
-        j_begin = split * per * MMA_BN;
-        j_end = min(kmax, (split + 1) * per * MMA_BN);
+        const int tiles = (kmax + MMA_BN - 1) / MMA_BN - t_lo, per = (tiles + splits - 1) / splits;
+        j_begin = (t_lo + split * per) * MMA_BN;
+        j_end = min(kmax, (t_lo + (split + 1) * per) * MMA_BN);
     }
     // ---- stage one tile of cache rows: a warp per row (one page lookup), lanes over 16-byte pieces ----
     // a tile that lies inside one page (pages are multiples of the tile, tiles start at multiples of it) needs one lookup
@@ -383,6 +396,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         __syncthreads();
         const uint32_t kt_base = ks_base + (uint32_t)(buf * MMA_BN * DS * 2);
         if (!warp_live || j0 + koff > warp_pos_max) continue;
+        if (window > 0 && j0 + koff + NKT * 8 - 1 <= warp_pos_lo - window) continue;      // below every row's window
         // ---- S = Q K^T (16 rows x NKT * 8 keys per warp) ----
         float sc[NKT][4];
 #pragma unroll
@@ -404,7 +418,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         // ---- mask, online softmax ----
         float mx[2] = {m_run[0], m_run[1]};
         // tiles wholly behind every row of this warp (the bulk of a long portion) need no mask
-        const bool all_visible = j0 + koff + NKT * 8 - 1 <= warp_pos_min;
+        const bool all_visible = j0 + koff + NKT * 8 - 1 <= warp_pos_min && (window <= 0 || j0 + koff > warp_pos_max - window);
         if (all_visible) {
 #pragma unroll
             for (int n = 0; n < NKT; ++n)
@@ -420,7 +434,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
                 for (int e = 0; e < 4; ++e) {
                     const int key = j0 + koff + n * 8 + 2 * t4 + (e & 1);
                     const int k = e >> 1;
-                    const float v = (key <= pos_row[k]) ? sc[n][e] * scale : -INFINITY;
+                    const float v = (key <= pos_row[k] && (window <= 0 || pos_row[k] - key < window)) ? sc[n][e] * scale : -INFINITY;
                     sc[n][e] = v;
                     mx[k] = fmaxf(mx[k], v);
                 }
@@ -512,7 +526,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(
         const int rr = row0 + warp * 16 + g + 8 * k;
         if (rr >= nrows) continue;
         const int i = rr / H, h = rr - i * H;
-        const float inv = 1.0f / l_run[k];
+        const float inv = l_run[k] > 0.f ? 1.0f / l_run[k] : 0.f;
         __nv_bfloat16* dst = out + ((int64_t)h * total_q + sp.q0 + i) * rank;
 #pragma unroll
         for (int n = 0; n < NT_O; ++n) {
@@ -535,7 +549,7 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
     for (int p = 0; p < splits; ++p) M = fmaxf(M, base[p * step + rank]);
     float L = 0.f;
     for (int p = 0; p < splits; ++p) L += __expf(base[p * step + rank] - M) * base[p * step + rank + 1];
-    const float inv = 1.0f / L;
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float a = 0.f;
         for (int p = 0; p < splits; ++p) a = fmaf(__expf(base[p * step + rank] - M), base[p * step + c], a);
@@ -544,10 +558,10 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restri
 }
 
 template <int NT_O, bool WS, int BN>
-int launch_attn_mma_bn(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+int launch_attn_mma_bn(const void* q_lat, const void* q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off, const void* cache,
                     const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
                     const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
-                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
+                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int window, int layout, int splits, float* part, cudaStream_t stream) {
     const int DS = mma_row_stride(rank + rot_dim);
     if (splits < 1 || max_q != 1 || cu_q != nullptr || part == nullptr || H > MMA_BM) splits = 1;
     const size_t smem = (size_t)(WS ? 16 + 2 * BN : MMA_BM + BN) * DS * sizeof(__nv_bfloat16);       // as the kernel lays it out
@@ -556,8 +570,8 @@ int launch_attn_mma_bn(const void* q_lat, const void* q_raw, int q_head_stride, 
     dim3 grid((max_q * H + MMA_BM - 1) / MMA_BM, num_seqs, ((rank + NT_O * 8 - 1) / (NT_O * 8)) * splits);
     using bf = __nv_bfloat16;
     B200_LAUNCH((latent_attn_mma_kernel<NT_O, WS, BN>), grid, 128, smem, stream, static_cast<const bf*>(q_lat), static_cast<const bf*>(q_raw),
-                q_head_stride, q_rot_off, static_cast<const bf*>(cache), block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens,
-                sink, cos_sin, rope_dims, static_cast<bf*>(out), total_q, H, rank, rot_dim, scale, splits, part);
+                q_tok_stride, q_head_stride, q_rot_off, static_cast<const bf*>(cache), block_tables, bt_stride, block_size, cu_q, cu_k, ctx_lens,
+                sink, cos_sin, rope_dims, static_cast<bf*>(out), total_q, H, rank, rot_dim, scale, window, layout, splits, part);
     rc = b200_launch_status(nullptr);
     if (rc != B200_OK || splits == 1) return rc;
     B200_LAUNCH((latent_merge_kernel), dim3(num_seqs, H), 128, 0, stream, (const float*)part, ctx_lens, WS ? splits * 4 : splits, H, rank,
@@ -566,55 +580,56 @@ int launch_attn_mma_bn(const void* q_lat, const void* q_raw, int q_head_stride, 
 }
 
 template <int NT_O, bool WS>
-int launch_attn_mma_ws(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+int launch_attn_mma_ws(const void* q_lat, const void* q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off, const void* cache,
                        const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
                        const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
-                       int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
+                       int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int window, int layout, int splits, float* part, cudaStream_t stream) {
     // 64-key tiles while two CTAs of (64 + 64) staged rows fit in an SM; 32-key tiles for wider rows
     const bool narrow = !WS && (size_t)(MMA_BM + 64) * mma_row_stride(rank + rot_dim) * sizeof(__nv_bfloat16) > 112 * 1024;
     if (narrow)
-        return launch_attn_mma_bn<NT_O, false, 32>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+        return launch_attn_mma_bn<NT_O, false, 32>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
                                                    ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale,
-                                                   splits, part, stream);
-    return launch_attn_mma_bn<NT_O, WS, 64>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                            ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale, splits,
-                                            part, stream);
+                                                   window, layout, splits, part, stream);
+    return launch_attn_mma_bn<NT_O, WS, 64>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                            ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale, window, layout,
+                                            splits, part, stream);
 }
 
 template <int NT_O>
-int launch_attn_mma(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+int launch_attn_mma(const void* q_lat, const void* q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off, const void* cache,
                     const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q, const int32_t* cu_k,
                     const int32_t* ctx_lens, const float* sink, const float* cos_sin, int rope_dims, void* out, int total_q,
-                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int splits, float* part, cudaStream_t stream) {
+                    int num_seqs, int max_q, int H, int rank, int rot_dim, float scale, int window, int layout, int splits, float* part, cudaStream_t stream) {
     if (splits > 1 && max_q == 1 && cu_q == nullptr && part != nullptr && H <= 16)
-        return launch_attn_mma_ws<NT_O, true>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+        return launch_attn_mma_ws<NT_O, true>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
                                               ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale,
-                                              splits, part, stream);
-    return launch_attn_mma_ws<NT_O, false>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                              window, layout, splits, part, stream);
+    return launch_attn_mma_ws<NT_O, false>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
                                            ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, H, rank, rot_dim, scale,
-                                           splits, part, stream);
+                                           window, layout, splits, part, stream);
 }
 
 }  // namespace
 
 extern "C" int b200m_latent_store(const void* dkv, int64_t stride, const void* norm_w, const float* cos_sin, int rope_dims,
                                   const int64_t* positions, const int32_t* slots, void* cache, int n, int rank, int rot_dim,
-                                  float eps, int is32, void* stream) {
+                                  float eps, int layout, int is32, void* stream) {
     if (!dkv || !norm_w || !cos_sin || !positions || !slots || !cache || n < 0 || rank <= 0 || rot_dim < 0) return B200_EINVAL;
     if (rope_dims < 0 || rope_dims > rot_dim || (rope_dims & 1)) return B200_EINVAL;
     if (n == 0) return B200_OK;
     B200M_DISPATCH(is32, B200_LAUNCH((latent_store_kernel<T>), n, 128, 0, static_cast<cudaStream_t>(stream),
                                      static_cast<const T*>(dkv), stride, static_cast<const T*>(norm_w), cos_sin, rope_dims,
-                                     positions, slots, static_cast<T*>(cache), rank, rot_dim, eps));
+                                     positions, slots, static_cast<T*>(cache), rank, rot_dim, eps, layout));
     return b200_launch_status(nullptr);
 }
 
-extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int q_head_stride, int q_rot_off, const void* cache,
+extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int64_t q_tok_stride, int q_head_stride, int q_rot_off, const void* cache,
                                       const int32_t* block_tables, int bt_stride, int block_size, const int32_t* cu_q,
                                       const int32_t* cu_k, const int32_t* ctx_lens, const float* sink, const float* cos_sin,
                                       int rope_dims, void* out, int total_q, int num_seqs, int max_q, int num_heads, int rank,
-                                      int rot_dim, float scale, int is32, int flags, int splits, float* part, void* stream) {
-    if (!q_lat || !q_raw || !cache || !block_tables || !sink || !cos_sin || !out) return B200_EINVAL;
+                                      int rot_dim, float scale, int window, int layout, int is32, int flags, int splits, float* part,
+                                      void* stream) {
+    if (!q_lat || !q_raw || !cache || !block_tables || !cos_sin || !out) return B200_EINVAL;
     if ((cu_q == nullptr) != (cu_k == nullptr) || (cu_q == nullptr && ctx_lens == nullptr)) return B200_EINVAL;
     if (total_q < 0 || num_seqs < 0 || num_heads <= 0 || rank <= 0 || rot_dim < 0 || block_size <= 0) return B200_EINVAL;
     if (rope_dims < 0 || rope_dims > rot_dim || (rope_dims & 1)) return B200_EINVAL;
@@ -623,15 +638,15 @@ extern "C" int b200m_latent_attention(const void* q_lat, const void* q_raw, int 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (!is32 && !(flags & 1)) {         // bf16: tensor cores; 128 output columns per CTA when the latent fits, else 256 per pass
         if (rank <= 128)
-            return launch_attn_mma<16>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                       ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, splits, part, st);
-        return launch_attn_mma<32>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
-                                   ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, splits, part, st);
+            return launch_attn_mma<16>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                       ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, window, layout, splits, part, st);
+        return launch_attn_mma<32>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride, block_size, cu_q, cu_k,
+                                   ctx_lens, sink, cos_sin, rope_dims, out, total_q, num_seqs, max_q, num_heads, rank, rot_dim, scale, window, layout, splits, part, st);
     }
 #define LA_GO(N)                                                                                                              \
-    B200M_DISPATCH(is32, return (launch_attn<T, N>(q_lat, q_raw, q_head_stride, q_rot_off, cache, block_tables, bt_stride,     \
+    B200M_DISPATCH(is32, return (launch_attn<T, N>(q_lat, q_raw, q_tok_stride, q_head_stride, q_rot_off, cache, block_tables, bt_stride,     \
                                                    block_size, cu_q, cu_k, ctx_lens, sink, cos_sin, rope_dims, out, total_q,  \
-                                                   num_seqs, max_q, num_heads, rank, rot_dim, scale, st)))
+                                                   num_seqs, max_q, num_heads, rank, rot_dim, scale, window, layout, st)))
     if (rank <= 128) LA_GO(4);
     if (rank <= 256) LA_GO(8);
     LA_GO(16);

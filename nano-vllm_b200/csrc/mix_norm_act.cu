@@ -231,9 +231,148 @@ __global__ void __launch_bounds__(256) ff_act_vec_kernel(const __nv_bfloat16* __
     *reinterpret_cast<uint4*>(out + r * n + c) = pack8(o);
 }
 
+// Gated unit with clamped branches: x = [gate | up] per row, g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1).
+__device__ __forceinline__ float glu_clamped_(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoidf_(alpha * g) * (u + 1.0f);
+}
+
+template <typename T>
+__global__ void ff_glu_clamped_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ out, int64_t rows, int n, float limit,
+                                      float alpha) {
+    B200_PDL_SYNC();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * n) return;
+    const int64_t r = i / n;
+    const int c = (int)(i - r * n);
+    stf(out + i, glu_clamped_(ldf(x + r * x_stride + c), ldf(x + r * x_stride + n + c), limit, alpha));
+}
+
+__global__ void __launch_bounds__(256) ff_glu_clamped_vec_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, __nv_bfloat16* __restrict__ out, int n,
+                                                                 float limit, float alpha) {
+    B200_PDL_SYNC();
+    const int c = (blockIdx.x * 256 + threadIdx.x) << 3;
+    if (c >= n) return;
+    const int64_t r = blockIdx.y;
+    float gt[8], up[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + r * x_stride + c), gt);
+    unpack8(*reinterpret_cast<const uint4*>(x + r * x_stride + n + c), up);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = glu_clamped_(gt[e], up[e], limit, alpha);
+    *reinterpret_cast<uint4*>(out + r * n + c) = pack8(o);
+}
+
+// A sublayer's close in a layer that gates, norms and column-scales the sublayer's result:
+//     t = y * sigmoid(gate);  x += t / sqrt(mean(t^2) + eps) * w_out;  out_next = x / sqrt(mean(x^2) + eps) * next_scale * w_next.
+// The gated row stays in registers between the statistic and the update (PER elements per thread; wider rows are recomputed).
+template <typename T, int PER>
+__global__ void __launch_bounds__(ROW_THREADS) gated_add_normed_kernel(float* __restrict__ x, const T* __restrict__ y,
+                                                                       const float* __restrict__ y32, const T* __restrict__ gate,
+                                                                       int64_t gate_stride, const float* __restrict__ w_out,
+                                                                       const float* __restrict__ w_next, float next_scale,
+                                                                       T* __restrict__ out_next, int cols, float eps) {
+    B200_PDL_SYNC();
+    __shared__ float red[ROW_THREADS / 32];
+    const int64_t base = (int64_t)blockIdx.x * cols;
+    const T* grow = gate ? gate + (int64_t)blockIdx.x * gate_stride : nullptr;
+    auto gated = [&](int c) {
+        const float v = y32 ? y32[base + c] : ldf(y + base + c);
+        return grow ? v * sigmoidf_(ldf(grow + c)) : v;
+    };
+    float t[PER];
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = threadIdx.x + k * ROW_THREADS;
+        t[k] = c < cols ? gated(c) : 0.f;
+        q = fmaf(t[k], t[k], q);
+    }
+    for (int c = threadIdx.x + PER * ROW_THREADS; c < cols; c += ROW_THREADS) {
+        const float v = gated(c);
+        q = fmaf(v, v, q);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)cols + eps);
+    float q2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = threadIdx.x + k * ROW_THREADS;
+        if (c < cols) {
+            t[k] = fmaf(t[k] * rstd, w_out[c], x[base + c]);
+            x[base + c] = t[k];
+            q2 = fmaf(t[k], t[k], q2);
+        }
+    }
+    for (int c = threadIdx.x + PER * ROW_THREADS; c < cols; c += ROW_THREADS) {
+        const float r = fmaf(gated(c) * rstd, w_out[c], x[base + c]);
+        x[base + c] = r;
+        q2 = fmaf(r, r, q2);
+    }
+    if (out_next == nullptr) return;
+    const float rstd2 = next_scale / sqrtf(block_sum(q2, red) / (float)cols + eps);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int c = threadIdx.x + k * ROW_THREADS;
+        if (c < cols) stf(out_next + base + c, t[k] * rstd2 * (w_next ? w_next[c] : 1.0f));
+    }
+    for (int c = threadIdx.x + PER * ROW_THREADS; c < cols; c += ROW_THREADS)      // the same thread wrote these elements
+        stf(out_next + base + c, x[base + c] * rstd2 * (w_next ? w_next[c] : 1.0f));
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap) {
+    B200_PDL_SYNC();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
 }  // namespace
 
-extern "C" int b200m_abi_version(void) { return 3; }
+extern "C" int b200m_abi_version(void) { return 4; }
+
+extern "C" int b200m_ff_glu_clamped(const void* x, int64_t x_stride, void* out, int64_t rows, int n, float limit, float alpha, int is32,
+                                    void* stream) {
+    if (!x || !out || rows < 0 || n <= 0 || x_stride < 2 * (int64_t)n) return B200_EINVAL;
+    if (rows == 0) return B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!is32 && n % 8 == 0 && x_stride % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        for (int64_t r0 = 0; r0 < rows; r0 += 65535) {             // grid.y limit
+            const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
+            B200_LAUNCH((ff_glu_clamped_vec_kernel), dim3((n / 8 + 255) / 256, (unsigned)nr), 256, 0, st,
+                        static_cast<const __nv_bfloat16*>(x) + r0 * x_stride, x_stride, static_cast<__nv_bfloat16*>(out) + r0 * n, n, limit, alpha);
+        }
+        return b200_launch_status(nullptr);
+    }
+    const int64_t total = rows * n;
+    B200M_DISPATCH(is32, B200_LAUNCH((ff_glu_clamped_kernel<T>), (unsigned)((total + 255) / 256), 256, 0, st, static_cast<const T*>(x),
+                                     x_stride, static_cast<T*>(out), rows, n, limit, alpha));
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_gated_add_normed_norm(float* x, const void* y, const float* y32, const void* gate, int64_t gate_stride,
+                                           const float* w_out, const float* w_next, float next_scale, void* out_next, int rows,
+                                           int cols, float eps, int is32, void* stream) {
+    if (!x || (!y && !y32) || !w_out || rows < 0 || cols <= 0) return B200_EINVAL;
+    if (rows == 0) return B200_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cols <= 4 * ROW_THREADS) {
+        B200M_DISPATCH(is32, B200_LAUNCH((gated_add_normed_kernel<T, 4>), rows, ROW_THREADS, 0, st, x, static_cast<const T*>(y), y32,
+                                         static_cast<const T*>(gate), gate_stride, w_out, w_next, next_scale, static_cast<T*>(out_next),
+                                         cols, eps));
+    } else {
+        B200M_DISPATCH(is32, B200_LAUNCH((gated_add_normed_kernel<T, 16>), rows, ROW_THREADS, 0, st, x, static_cast<const T*>(y), y32,
+                                         static_cast<const T*>(gate), gate_stride, w_out, w_next, next_scale, static_cast<T*>(out_next),
+                                         cols, eps));
+    }
+    return b200_launch_status(nullptr);
+}
+
+extern "C" int b200m_softcap(float* x, int64_t n, float cap, void* stream) {
+    if (!x || n < 0 || !(cap > 0.f)) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    B200_LAUNCH((softcap_kernel), (unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), x, n, cap);
+    return b200_launch_status(nullptr);
+}
 
 extern "C" int b200m_embed(const int64_t* ids, const void* table, float* out, void* copy, int n, int width, int64_t vocab, int is32,
                            void* stream) {

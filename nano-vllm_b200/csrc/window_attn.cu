@@ -762,14 +762,15 @@ template <typename T>
 __global__ void __launch_bounds__(128) headnorm_rope_store_kernel(T* __restrict__ x, int64_t stride, int q_off, int k_off, int v_off, int H,
                                                                   int G, int dim, int vdim, const T* __restrict__ wq,
                                                                   const T* __restrict__ wk, int v_unit, const float* __restrict__ cos_sin,
-                                                                  int rope_dims, const int64_t* __restrict__ positions,
+                                                                  int rope_dims, const float* __restrict__ v_cos_sin, int v_rope_dims,
+                                                                  const int64_t* __restrict__ positions,
                                                                   const int32_t* __restrict__ slots, T* __restrict__ cache, float eps) {
     B200_PDL_SYNC();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     T* row = x + (int64_t)t * stride;
     const int slot = slots ? slots[t] : -1;
     const float* cs = cos_sin ? cos_sin + positions[t] * rope_dims : nullptr;
-    const int half = rope_dims / 2;
+    const float* vcs = v_cos_sin ? v_cos_sin + positions[t] * v_rope_dims : nullptr;
     T* crow = (cache && slot >= 0) ? cache + (int64_t)slot * ((int64_t)G * (dim + vdim)) : nullptr;
     for (int r = warp; r < H + 2 * G; r += nw) {
         const bool is_q = r < H, is_k = !is_q && r < H + G;
@@ -789,7 +790,10 @@ __global__ void __launch_bounds__(128) headnorm_rope_store_kernel(T* __restrict_
             }
             rstd = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
         }
-        const bool rot = cs != nullptr && (is_q || is_k);
+        // queries and keys turn by one table, values (when asked for) by their own, over their own width
+        const float* rcs = (is_q || is_k) ? cs : vcs;
+        const bool rot = rcs != nullptr;
+        const int half = ((is_q || is_k) ? rope_dims : v_rope_dims) / 2;
         for (int c = 2 * lane; c < d; c += 64) {           // a lane owns whole pairs
             float a = ldf(src + c) * rstd, b = c + 1 < d ? ldf(src + c + 1) * rstd : 0.f;
             if (w) {
@@ -798,7 +802,7 @@ __global__ void __launch_bounds__(128) headnorm_rope_store_kernel(T* __restrict_
             }
             const int i = c >> 1;
             if (rot && i < half) {
-                const float co = cs[i], si = cs[half + i];
+                const float co = rcs[i], si = rcs[half + i];
                 const float ra = a * co - b * si, rb = b * co + a * si;
                 a = ra;
                 b = rb;
@@ -808,6 +812,72 @@ __global__ void __launch_bounds__(128) headnorm_rope_store_kernel(T* __restrict_
         }
     }
 }
+
+// out[t, h, :] = rotate(acc[t, h, :], sign * position) * sigmoid(gate[t, h, :]): a thread per pair of elements of a head.
+template <typename T, typename A>
+__global__ void __launch_bounds__(256) head_rotate_gate_kernel(const A* __restrict__ acc, int64_t acc_tok_stride, int64_t acc_head_stride,
+                                                               const float* __restrict__ cos_sin, int rope_dims, int layout, float sign,
+                                                               const int64_t* __restrict__ positions, const T* __restrict__ gate,
+                                                               int64_t gate_stride, T* __restrict__ out, int64_t out_stride, int H, int vdim) {
+    B200_PDL_SYNC();
+    const int64_t t = blockIdx.x;
+    const int half = rope_dims / 2, pairs = (vdim + 1) / 2;
+    const float* cs = cos_sin ? cos_sin + positions[t] * rope_dims : nullptr;
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < H * pairs; e += gridDim.y * blockDim.x) {
+        const int h = e / pairs, p = e - h * pairs;
+        // pair p of the head: rotated pairs first (p < half), then the elements past rope_dims two at a time
+        int e0, e1;
+        if (p < half) {
+            e0 = layout ? p : 2 * p;
+            e1 = layout ? p + half : 2 * p + 1;
+        } else {
+            e0 = rope_dims + 2 * (p - half);
+            e1 = e0 + 1;
+        }
+        const A* a = acc + t * acc_tok_stride + (int64_t)h * acc_head_stride;
+        float u = ldf(a + e0), v = e1 < vdim ? ldf(a + e1) : 0.f;
+        if (cs != nullptr && p < half) {
+            const float co = cs[p], si = sign * cs[half + p];
+            const float ru = u * co - v * si, rv = v * co + u * si;
+            u = ru;
+            v = rv;
+        }
+        const int64_t o = (int64_t)h * vdim;
+        if (gate) {
+            u *= sigmoidf_(ldf(gate + t * gate_stride + o + e0));
+            if (e1 < vdim) v *= sigmoidf_(ldf(gate + t * gate_stride + o + e1));
+        }
+        stf(out + t * out_stride + o + e0, u);
+        if (e1 < vdim) stf(out + t * out_stride + o + e1, v);
+    }
+}
+
+}  // namespace
+
+extern "C" int b200m_head_rotate_gate(const void* acc, int acc_f32, int64_t acc_tok_stride, int64_t acc_head_stride, const float* cos_sin,
+                                      int rope_dims, int layout, float sign, const int64_t* positions, const void* gate, int64_t gate_stride,
+                                      void* out, int64_t out_stride, int n, int num_heads, int vdim, int is32, void* stream) {
+    if (!acc || !out || n < 0 || num_heads <= 0 || vdim <= 0 || rope_dims < 0 || rope_dims > vdim || (rope_dims & 1)) return B200_EINVAL;
+    if (cos_sin && rope_dims > 0 && !positions) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    if (rope_dims == 0) cos_sin = nullptr;
+    if (cos_sin == nullptr) rope_dims = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int work = num_heads * ((vdim + 1) / 2);
+    dim3 grid(n, (unsigned)((work + 1023) / 1024));                 // up to four pairs per thread
+    if (is32 || acc_f32) {
+        B200M_DISPATCH(is32, B200_LAUNCH((head_rotate_gate_kernel<T, float>), grid, 256, 0, st, static_cast<const float*>(acc), acc_tok_stride,
+                                         acc_head_stride, cos_sin, rope_dims, layout, sign, positions, static_cast<const T*>(gate), gate_stride,
+                                         static_cast<T*>(out), out_stride, num_heads, vdim));
+    } else {
+        B200_LAUNCH((head_rotate_gate_kernel<__nv_bfloat16, __nv_bfloat16>), grid, 256, 0, st, static_cast<const __nv_bfloat16*>(acc),
+                    acc_tok_stride, acc_head_stride, cos_sin, rope_dims, layout, sign, positions, static_cast<const __nv_bfloat16*>(gate),
+                    gate_stride, static_cast<__nv_bfloat16*>(out), out_stride, num_heads, vdim);
+    }
+    return b200_launch_status(nullptr);
+}
+
+namespace {
 
 // One thread per (value head v, VEC columns) of a token: it reads head g's accumulator for that value head once and feeds the
 // H / G output heads that own value head v (eight at a time), so every accumulator element is read once.  The mixing matrix
@@ -868,16 +938,18 @@ __global__ void __launch_bounds__(256) head_mix_gate_kernel(const A* __restrict_
 
 extern "C" int b200m_headnorm_rope_store(void* x, int64_t stride, int q_off, int k_off, int v_off, int num_heads, int num_kv_heads, int dim,
                                          int vdim, const void* q_norm_w, const void* k_norm_w, int v_unit_norm, const float* cos_sin,
-                                         int rope_dims, const int64_t* positions, const int32_t* slots, void* cache, int n, float eps,
-                                         int is32, void* stream) {
+                                         int rope_dims, const float* v_cos_sin, int v_rope_dims, const int64_t* positions,
+                                         const int32_t* slots, void* cache, int n, float eps, int is32, void* stream) {
     if (!x || n < 0 || num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 || rope_dims < 0 || rope_dims > dim || (rope_dims & 1))
         return B200_EINVAL;
     if ((cos_sin && rope_dims > 0 && !positions) || (cache && !slots)) return B200_EINVAL;
+    if (v_rope_dims < 0 || v_rope_dims > vdim || (v_rope_dims & 1) || (v_cos_sin && v_rope_dims > 0 && !positions)) return B200_EINVAL;
+    if (v_rope_dims == 0) v_cos_sin = nullptr;
     if (n == 0) return B200_OK;
     if (rope_dims == 0) cos_sin = nullptr;
     B200M_DISPATCH(is32, B200_LAUNCH((headnorm_rope_store_kernel<T>), n, 128, 0, static_cast<cudaStream_t>(stream), static_cast<T*>(x), stride,
                                      q_off, k_off, v_off, num_heads, num_kv_heads, dim, vdim, static_cast<const T*>(q_norm_w),
-                                     static_cast<const T*>(k_norm_w), v_unit_norm, cos_sin, rope_dims, positions, slots,
+                                     static_cast<const T*>(k_norm_w), v_unit_norm, cos_sin, rope_dims, v_cos_sin, v_rope_dims, positions, slots,
                                      static_cast<T*>(cache), eps));
     return b200_launch_status(nullptr);
 }

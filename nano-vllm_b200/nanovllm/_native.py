@@ -57,7 +57,11 @@ MIX_SIGNATURES = {
                                     _f, _i, _i, _i, _vp, _vp]),
     "b200m_embed_pair": (_i, [_vp, _vp, _f, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp]),
     "b200m_add_normed_norm": (_i, [_vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _f, _vp, _i, _i, _f, _i, _vp]),
-    "b200m_headnorm_rope_store": (_i, [_vp, _i64, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _i, _vp]),
+    "b200m_headnorm_rope_store": (_i, [_vp, _i64, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _f, _i, _vp]),
+    "b200m_head_rotate_gate": (_i, [_vp, _i, _i64, _i64, _vp, _i, _i, _f, _vp, _vp, _i64, _vp, _i64, _i, _i, _i, _i, _vp]),
+    "b200m_gated_add_normed_norm": (_i, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _f, _vp, _i, _i, _f, _i, _vp]),
+    "b200m_ff_glu_clamped": (_i, [_vp, _i64, _vp, _i64, _i, _f, _f, _i, _vp]),
+    "b200m_softcap": (_i, [_vp, _i64, _f, _vp]),
     "b200m_head_mix_gate": (_i, [_vp, _i, _vp, _vp, _i64, _vp, _i64, _f, _i, _i, _i, _i, _i, _vp]),
     "b200m_diag_scan": (_i, [_vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp]),
     "b200m_gated_delta": (_i, [_vp, _i64, _i, _i, _i, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
@@ -66,9 +70,9 @@ MIX_SIGNATURES = {
     "b200m_add_layernorm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "b200m_rmsnorm": (_i, [_vp, _i64, _vp, _vp, _i64, _i, _i, _f, _i, _vp]),
     "b200m_ff_act": (_i, [_vp, _vp, _i64, _i, _i, _i, _vp]),
-    "b200m_latent_store": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
-    "b200m_latent_attention": (_i, [_vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
-                                    _f, _i, _i, _i, _vp, _vp]),
+    "b200m_latent_store": (_i, [_vp, _i64, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
+    "b200m_latent_attention": (_i, [_vp, _vp, _i64, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i,
+                                    _f, _i, _i, _i, _i, _i, _vp, _vp]),
     "b200m_causal_conv": (_i, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "b200m_selective_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i,
                                   _vp]),

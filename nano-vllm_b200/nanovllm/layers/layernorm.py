@@ -70,3 +70,45 @@ class SandwichNorm:
         from .. import mixops
         return mixops.add_normed_norm(x, y, self.w_out, self.eps, w_offset=1.0, next_weight=then.w_in if then is not None else None,
                                       next_offset=1.0, copy=copy)
+
+
+class GatedScaledSandwich:
+    """The norms, gate and column scale around one sublayer of a block that reads a normed stream and gates, norms and scales the
+    sublayer's result:
+
+        h = rms(x) * g_in                          (g_in, g_out: ONE number each)
+        x <- x + ls * rms(f(h) * sigmoid(W_r h + b_r)) * g_out
+
+    over an fp32 stream.  The gate's pre-activation ``W_r h + b_r`` comes from the sublayer (its rows ride in the sublayer's input
+    projection, which reads the same h).  ``g_out * ls`` is folded into one fp32 vector when either is loaded; ``g_in`` is kept as a
+    vector in the activation type (the opening norm of a step) and in fp32 (the opening norm fused into the previous close)."""
+
+    def __init__(self, width: int, eps: float, dtype, device):
+        self.eps, self.dtype = eps, dtype
+        self.g_out = torch.ones(1, dtype=torch.float32, device=device)
+        self.ls = torch.ones(width, dtype=torch.float32, device=device)
+        self.w_out = torch.ones(width, dtype=torch.float32, device=device)        # g_out * ls
+        self.w_in32 = torch.ones(width, dtype=torch.float32, device=device)       # g_in on every column
+        self.w_in = torch.ones(width, dtype=dtype, device=device)
+
+    def load(self, which: str, w: torch.Tensor) -> None:
+        w = w.to(self.w_out.device, torch.float32).reshape(-1)
+        if which == "in":
+            self.w_in32.copy_(w.expand_as(self.w_in32))
+            self.w_in.copy_(self.w_in32)
+            return
+        if which == "out":
+            self.g_out.copy_(w)
+        else:
+            self.ls.copy_(w)
+        torch.mul(self.ls, self.g_out, out=self.w_out)
+
+    def open(self, x):
+        from .. import mixops
+        return mixops.rmsnorm_rows(x, self.w_in, self.eps)
+
+    def close(self, x, y, gate, then: "GatedScaledSandwich | None" = None):
+        """x += ls * norm_out(y * sigmoid(gate)); with ``then`` also returns that sublayer's normed input."""
+        from .. import mixops
+        return mixops.gated_add_normed_norm(x, y, gate, self.w_out, self.eps, self.dtype, next_scale=1.0 if then is not None else None,
+                                            w_next=then.w_in32 if then is not None else None)

@@ -13,6 +13,12 @@ Group-routed (``GroupRoutedExpertsFF``):
          out = sum_e w_e expert_e(h),  expert(x) = W_down (silu(W_gate x) * (W_up x));  the last `identity` router outputs are
          identity experts without tensors (expert(x) = x); an optional ungated shared expert of the same form is added.
 
+Clamped (``ClampedGluFF``):  g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit);  W_down (g sigmoid(alpha g) (u + 1)).
+
+Top-k by logit (``BiasedTopKExpertsFF``): z = W_router h + b_router (fp32); the `top` largest z are chosen and weighted with the
+         softmax over the chosen z alone (= the softmax over all, renormalised over the chosen, which is what the group-routed kernel
+         computes with one group and no correction); gated SiLU experts and an ungated shared expert as above.
+
 The routed path groups (token, choice) pairs by expert on the device and runs two grouped GEMMs over the grouped rows; the
 router (and the shared gate, one more row of the same fp32 GEMM) never leave fp32.
 """
@@ -138,6 +144,7 @@ class GroupRoutedExpertsFF:
         self.w_gate_up = e(max(self.experts, 1), 2 * self.ff, width)        # per expert: gate rows, then up rows
         self.w_down = e(max(self.experts, 1), width, self.ff)
         self.w_router = torch.zeros(self.outputs, width, dtype=torch.float32, device=device)
+        self.router_bias = None                                             # fp32 [outputs], added to the router logits
         self.correction = torch.zeros(self.outputs, dtype=torch.float32, device=device)
         if shared:
             self.sh_gate_up, self.sh_down = e(2 * self.shared_ff, width), e(width, self.shared_ff)
@@ -179,7 +186,7 @@ class GroupRoutedExpertsFF:
     def forward(self, h: torch.Tensor, x32: torch.Tensor) -> torch.Tensor:
         """h: the block's input in the activation type, x32: the same rows in fp32 (router input, identity experts) -> fp32."""
         n = h.shape[0]
-        logits = F.linear(x32, self.w_router)
+        logits = F.linear(x32, self.w_router, self.router_bias)
         idx, wgt = mixops.moe_route_grouped(logits, self.outputs, self.top, self.correction, self.groups, self.keep, self.experts,
                                             scale=self.route_scale)
         sorted_rows, pos_of, tile_expert, num_tiles = mixops.moe_align(idx, max(self.experts, 1))
@@ -189,3 +196,71 @@ class GroupRoutedExpertsFF:
         if self.shared_ff:
             shared = F.linear(mixops.ff_act(F.linear(h, self.sh_gate_up), mixops.FF_SILU_MUL), self.sh_down)
         return mixops.moe_combine(rows, pos_of, self.top, n, shared, None, wgt=wgt, ident=x32 if self.identity else None)
+
+
+class BiasedTopKExpertsFF(GroupRoutedExpertsFF):
+    """Routed gated-SiLU experts chosen by the largest router logits (weight matrix plus bias, fp32), weighted with the softmax over
+    the chosen logits only, plus an optional ungated shared expert.  ``extra_rows`` more rows ride in no projection here: the
+    block's gate is a GEMM of its own (``w_extra``, ``b_extra``), since the experts' inputs are gathered per expert."""
+
+    def __init__(self, width: int, mlp: dict, dtype, device, extra_rows: int = 0):
+        r = dict(mlp["router"])
+        for key in ("identity", "groups", "scale"):
+            r.pop(key, None)                                                 # one group, no identity experts, unit scale
+        super().__init__(width, {**mlp, "router": r}, dtype, device)
+        self.router_bias = torch.zeros(self.outputs, dtype=torch.float32, device=device)
+        self.dtype = dtype
+        self.w_extra = torch.empty(extra_rows, width, dtype=dtype, device=device) if extra_rows else None
+        self.b_extra = torch.zeros(extra_rows, dtype=dtype, device=device) if extra_rows else None
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        if leaf == "router.b":
+            self.router_bias.copy_(w.float().view(-1))
+            return True
+        if leaf == "correction":
+            return False
+        return super().load(leaf, w)
+
+    def weight_shapes(self, width: int) -> dict:
+        out = super().weight_shapes(width)
+        del out["correction"]
+        out["router.b"] = (self.outputs,)
+        return out
+
+    def forward(self, h: torch.Tensor):
+        """-> (fp32 [n, width], the extra rows' projection of h or None)."""
+        y = super().forward(h, h if h.dtype == torch.float32 else h.float())
+        return y, (F.linear(h, self.w_extra, self.b_extra) if self.w_extra is not None else None)
+
+
+class ClampedGluFF:
+    """W_down (g * sigmoid(alpha * g) * (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit).  ``[W_gate ; W_up]`` and
+    ``extra_rows`` more rows (with a bias) that read the same input are one GEMM; ``forward`` returns the extra columns as a view."""
+
+    def __init__(self, width: int, mlp: dict, dtype, device, extra_rows: int = 0, alpha: float = 1.702):
+        self.ff, self.limit, self.alpha = int(mlp["ff"]), float(mlp["limit"]), float(mlp.get("alpha", alpha))
+        self.extra = extra_rows
+        self.w_in = torch.empty(2 * self.ff + extra_rows, width, dtype=dtype, device=device)
+        self.b_in = torch.zeros(2 * self.ff + extra_rows, dtype=dtype, device=device) if extra_rows else None
+        self.w_extra = self.w_in[2 * self.ff:] if extra_rows else None
+        self.b_extra = self.b_in[2 * self.ff:] if extra_rows else None
+        self.w_down = torch.empty(width, self.ff, dtype=dtype, device=device)
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        if leaf == "gate":
+            self.w_in[:self.ff].copy_(w)
+        elif leaf == "up":
+            self.w_in[self.ff:2 * self.ff].copy_(w)
+        elif leaf == "down":
+            self.w_down.copy_(w)
+        else:
+            return False
+        return True
+
+    def weight_shapes(self, width: int) -> dict:
+        return {"gate": (self.ff, width), "up": (self.ff, width), "down": (width, self.ff)}
+
+    def forward(self, h: torch.Tensor):
+        proj = F.linear(h, self.w_in, self.b_in)
+        y = F.linear(mixops.ff_glu_clamped(proj[:, :2 * self.ff], self.limit, self.alpha), self.w_down)
+        return y, (proj[:, 2 * self.ff:] if self.extra else None)

@@ -46,3 +46,27 @@ def build_interleaved_cos_sin(dims: int, max_position: int, base: float, scaling
     angles = torch.outer(torch.arange(max_position, dtype=torch.float64), freq)
     table = (torch.cat((angles.cos(), angles.sin()), dim=-1) * magnitude).to(torch.float32).contiguous()
     return table.to(device) if device is not None else table
+
+
+def banded_frequencies(dims: int, base: float, scaling: dict | None = None) -> torch.Tensor:
+    """float64 [dims / 2]: f_i = base^(-2i / dims).  ``scaling`` = {factor, low, high, original} rescales by wavelength bands
+    (w = 2 pi / f): short waves (w < original / high) keep f, long ones (w > original / low) turn at f / factor, and in between the two
+    are blended with s = (original / w - low) / (high - low): (1 - s) f / factor + s f."""
+    import math
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    freq = float(base) ** (-2.0 * i / dims)
+    if scaling:
+        factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+        wave = 2.0 * math.pi / freq
+        s = (original / wave - low) / (high - low)
+        blended = (1.0 - s) * freq / factor + s * freq
+        freq = torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, blended))
+    return freq
+
+
+def build_banded_cos_sin(dims: int, max_position: int, base: float, scaling: dict | None = None, device=None) -> torch.Tensor:
+    """fp32 ``[max_position, dims] = cat(cos, sin)`` of position * banded_frequencies: pair i of a rotated vector turns by column i
+    (which two elements form pair i is the consuming kernel's layout).  Angles are formed in float64 and rounded once."""
+    angles = torch.outer(torch.arange(max_position, dtype=torch.float64), banded_frequencies(dims, base, scaling))
+    table = torch.cat((angles.cos(), angles.sin()), dim=-1).to(torch.float32).contiguous()
+    return table.to(device) if device is not None else table

@@ -202,3 +202,103 @@ class MixedHeadWindowAttention:
 
     def forward(self, h: torch.Tensor, positions, ctx, spans: mixops.StepSpans, inst: int = 0) -> torch.Tensor:
         return F.linear(self.mix(F.linear(h, self.w_in, self.b_in), h, positions, ctx, spans, inst), self.w_o)
+
+
+class RotatedValueAttention:
+    """Grouped-query attention with per-head query/key norms, a banded partial pair rotation, and values that carry their own
+    position:
+
+        q = W_q h,  k = W_k h,  v = W_v h
+        q[h] <- rotate(rms(q[h]) * g_q, p),  k[g] <- rotate(rms(k[g]) * g_k, p)      (g_q, g_k: `dim` weights shared by the heads; the first
+                                                                                      rot.dims elements turn, pair (2i, 2i+1) by p * f_i, f_i banded)
+        v[g] at position j <- turn every pair (2m, 2m+1) of vdim by j * base^(-2m / vdim);   cached so
+        s[h, i, j] = (q_i[h] . k_j[h // (H / G)]) * scale,  visible j: j <= i (and i - j < window when the mask has a size)
+        o[h]_i = turn_back( sum_j softmax(s)_ij v_j, i )                                    (every pair by -i * base^(-2m / vdim))
+        out = W_o concat_h o[h]
+
+    One row ``[k (G * dim) | v (G * vdim)]`` per token, layer instance and page slot; keys after norm and rotation, values after
+    theirs.  The attention kernel leaves fp32 sums, which a row-wise kernel turns back and rounds once.  ``extra_rows`` more rows
+    (with a bias) that read the same input ride in the input projection; ``forward`` returns their columns as a view.
+    """
+    kind = "attention"
+
+    def __init__(self, width: int, m: dict, eps: float, dtype, device, max_position: int, extra_rows: int = 0):
+        from .rotary_embedding import build_banded_cos_sin
+        self.width, self.eps, self.dtype, self.device = width, eps, dtype, device
+        self.heads, self.kv_heads = int(m["heads"]), int(m["kv_heads"])
+        self.dim, self.vdim = int(m["dim"]), int(m["vdim"])
+        self.scale = float(m["scale"])
+        self.window = int((m.get("mask") or {}).get("size") or 0)           # 0: every earlier token is visible
+        if self.heads % self.kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        if self.vdim > 512:
+            raise ValueError(f"vdim {self.vdim}: the attention kernels hold at most 512 output columns per query row")
+        H, G, d, vd = self.heads, self.kv_heads, self.dim, self.vdim
+        self.q_cols, self.k_cols, self.v_cols = H * d, G * d, G * vd
+        self.in_cols, self.extra = self.q_cols + self.k_cols + self.v_cols, extra_rows
+        rot = m.get("rot")
+        self.cos_sin = self.v_cos_sin = None
+        self.rot_key = self.v_rot_key = None
+        if rot:
+            dims, base = int(rot.get("dims") or 0), float(rot["base"])
+            if dims > d or dims % 2 or vd % 2:
+                raise ValueError("rot.dims must be even and at most dim, and vdim even")
+            if dims > 0:
+                self.rot_key = ("pairs", dims, base, repr(rot.get("scaling")), max_position)
+                self.cos_sin = build_banded_cos_sin(dims, max_position, base, rot.get("scaling"), device)
+            self.v_rot_key = ("pairs", vd, base, "None", max_position)
+            self.v_cos_sin = build_banded_cos_sin(vd, max_position, base, None, device)
+        e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        self.w_in = e(self.in_cols + extra_rows, width)                    # [W_q ; W_k ; W_v ; extra]: one GEMM reads h once
+        self.b_in = torch.zeros(self.in_cols + extra_rows, dtype=dtype, device=device) if extra_rows else None
+        self.w_extra = self.w_in[self.in_cols:] if extra_rows else None
+        self.b_extra = self.b_in[self.in_cols:] if extra_rows else None
+        self.w_o = e(width, H * vd)
+        self.q_norm, self.k_norm = e(d), e(d)
+        self.cache: list = []                                              # per instance [num_blocks * block_size, G * (dim + vdim)]
+        self.block_size = 0
+
+    def load(self, leaf: str, w: torch.Tensor) -> bool:
+        q, k, v = self.q_cols, self.k_cols, self.v_cols
+        spans = {"q": (0, q), "k": (q, q + k), "v": (q + k, q + k + v)}
+        if leaf in spans:
+            self.w_in[spans[leaf][0]:spans[leaf][1]].copy_(w)
+        elif leaf == "q.norm":
+            self.q_norm.copy_(w)
+        elif leaf == "k.norm":
+            self.k_norm.copy_(w)
+        elif leaf == "o":
+            self.w_o.copy_(w)
+        else:
+            return False
+        return True
+
+    def weight_shapes(self, width: int) -> dict:
+        return {"q": (self.q_cols, width), "k": (self.k_cols, width), "v": (self.v_cols, width), "q.norm": (self.dim,), "k.norm": (self.dim,),
+                "o": (width, self.heads * self.vdim)}
+
+    def cache_row_elems(self) -> int:
+        return self.k_cols + self.v_cols
+
+    def state_slot_bytes(self) -> int:
+        return 0
+
+    def bind(self, num_blocks: int, block_size: int, num_slots: int, copies: int = 1) -> None:
+        self.block_size = block_size
+        self.cache = [torch.zeros(num_blocks * block_size, self.cache_row_elems(), dtype=self.dtype, device=self.device) for _ in range(copies)]
+
+    def unbind(self) -> None:
+        self.cache = []
+
+    def forward(self, h: torch.Tensor, positions, ctx, spans: mixops.StepSpans, inst: int = 0):
+        """-> (mixer output [n, width], the extra rows' projection of h (a view) or None)."""
+        n, q, k = h.shape[0], self.q_cols, self.k_cols
+        proj = F.linear(h, self.w_in, self.b_in)
+        cache = self.cache[inst]
+        mixops.headnorm_rope_store(proj, 0, q, q + k, self.heads, self.kv_heads, self.dim, self.vdim, self.q_norm, self.k_norm, False,
+                                   self.cos_sin, positions, ctx.slot_mapping, cache, self.eps, v_cos_sin=self.v_cos_sin)
+        acc = mixops.window_attention(proj, cache, ctx.block_tables, self.block_size, spans, self.heads, self.kv_heads, self.dim, self.vdim,
+                                      self.scale, None, self.window, out_f32=self.dtype != torch.float32)
+        o = mixops.head_rotate_gate(acc.view(n, self.heads, self.vdim), self.dtype, self.v_cos_sin, positions, sign=-1.0,
+                                    layout=mixops.ROT_PAIRS)
+        return F.linear(o, self.w_o), (proj[:, self.in_cols:] if self.extra else None)

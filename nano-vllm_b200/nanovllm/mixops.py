@@ -179,6 +179,41 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, cols: int | None 
 FF_GELU_TANH_MUL, FF_RELU2, FF_SILU_MUL, FF_GELU_TANH = 0, 1, 2, 3
 
 
+def ff_glu_clamped(x: torch.Tensor, limit: float, alpha: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [rows, 2n] = [gate | up] (a row-strided view) -> g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    assert x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 2 == 0
+    n = x.shape[1] // 2
+    if out is None:
+        out = torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
+    _call("b200m_ff_glu_clamped", x.data_ptr(), x.stride(0), out.data_ptr(), x.shape[0], n, float(limit), float(alpha), _is32(x), _stream())
+    return out
+
+
+def gated_add_normed_norm(x: torch.Tensor, y: torch.Tensor, gate: torch.Tensor | None, w_out: torch.Tensor, eps: float, dtype,
+                          next_scale: float | None = None, w_next: torch.Tensor | None = None):
+    """x (fp32 [rows, cols], in place) += rms_norm(y * sigmoid(gate)) * w_out; then, with ``next_scale``, returns
+    rms_norm(x) * next_scale * w_next in ``dtype`` (the next sublayer's input).  y: ``dtype`` or fp32, contiguous; gate: ``dtype``, a
+    row-strided view; w_out, w_next: fp32 [cols]."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2 and y.is_contiguous() and y.shape == x.shape
+    is32 = int(dtype == torch.float32)
+    y32 = y.dtype == torch.float32 and not is32
+    assert y32 or y.dtype == dtype
+    assert gate is None or (gate.dtype == dtype and gate.stride(1) == 1 and gate.shape == x.shape)
+    assert w_out.dtype == torch.float32 and w_out.numel() == x.shape[1] and (w_next is None or (w_next.dtype == torch.float32 and w_next.numel() == x.shape[1]))
+    out = torch.empty(x.shape, dtype=dtype, device=x.device) if next_scale is not None else None
+    _call("b200m_gated_add_normed_norm", x.data_ptr(), None if y32 else y.data_ptr(), y.data_ptr() if y32 else None, _p(gate),
+          gate.stride(0) if gate is not None else 0, w_out.data_ptr(), _p(w_next), float(next_scale or 0.0), _p(out), x.shape[0], x.shape[1],
+          eps, is32, _stream())
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x (fp32, contiguous) <- cap * tanh(x / cap), in place."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.is_cuda
+    _call("b200m_softcap", x.data_ptr(), x.numel(), float(cap), _stream())
+    return x
+
+
 def ff_act(x: torch.Tensor, kind: int, out: torch.Tensor | None = None) -> torch.Tensor:
     assert x.dim() == 2 and x.is_contiguous()
     n = x.shape[1] if kind in (FF_RELU2, FF_GELU_TANH) else x.shape[1] // 2
@@ -189,8 +224,11 @@ def ff_act(x: torch.Tensor, kind: int, out: torch.Tensor | None = None) -> torch
 
 
 # ---- latent attention ----------------------------------------------------------------------------------------------------
+ROT_PAIRS, ROT_HALVES = 0, 1          # which elements of a rotated vector form a pair: (2i, 2i+1) or (i, i + dims / 2)
+
+
 def latent_store(dkv: torch.Tensor, norm_w: torch.Tensor, cos_sin: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
-                 cache: torch.Tensor, rank: int, rot_dim: int, eps: float) -> None:
+                 cache: torch.Tensor, rank: int, rot_dim: int, eps: float, layout: int = ROT_PAIRS) -> None:
     """dkv [n, >= rank + rot_dim] -> cache rows [slots_total, rank + rot_dim] at ``slots`` (int32, -1 = skip)."""
     assert dkv.dim() == 2 and dkv.stride(1) == 1 and cache.is_contiguous() and cache.shape[-1] == rank + rot_dim
     assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous()
@@ -198,17 +236,18 @@ def latent_store(dkv: torch.Tensor, norm_w: torch.Tensor, cos_sin: torch.Tensor,
     is32 = _is32(dkv)
     _same(is32, norm_w, cache)
     _call("b200m_latent_store", dkv.data_ptr(), dkv.stride(0), norm_w.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1],
-          positions.data_ptr(), slots.data_ptr(), cache.data_ptr(), dkv.shape[0], rank, rot_dim, eps, is32, _stream())
+          positions.data_ptr(), slots.data_ptr(), cache.data_ptr(), dkv.shape[0], rank, rot_dim, eps, int(layout), is32, _stream())
 
 
 def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, cache: torch.Tensor, block_tables: torch.Tensor,
-                     block_size: int, spans: StepSpans, sink: torch.Tensor, cos_sin: torch.Tensor, scale: float,
-                     out: torch.Tensor | None = None, fma: bool = False) -> torch.Tensor:
-    """q_lat [H, n, rank], q_raw [n, H, head_stride] -> [H, n, rank].  bf16 runs on the tensor cores unless ``fma``."""
+                     block_size: int, spans: StepSpans, sink: torch.Tensor | None, cos_sin: torch.Tensor, scale: float,
+                     out: torch.Tensor | None = None, fma: bool = False, window: int = 0, layout: int = ROT_PAIRS) -> torch.Tensor:
+    """q_lat [H, n, rank], q_raw [n, H, >= q_rot_off + rot_dim] (any token / head strides) -> [H, n, rank].  bf16 runs on the tensor cores unless ``fma``.
+    ``sink`` None: ordinary softmax.  ``window`` > 0: a query sees itself and the window - 1 keys before it."""
     H, n, rank = q_lat.shape
     rot_dim = cache.shape[-1] - rank
-    assert q_lat.is_contiguous() and q_raw.is_contiguous() and q_raw.shape[:2] == (n, H) and cache.is_contiguous()
-    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and sink.dtype == torch.float32
+    assert q_lat.is_contiguous() and q_raw.stride(2) == 1 and q_raw.shape[:2] == (n, H) and cache.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and (sink is None or sink.dtype == torch.float32)
     is32 = _is32(q_lat)
     _same(is32, q_raw, cache)
     if out is None:
@@ -217,16 +256,17 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_rot_off: int, c
     # CTAs per SM are in flight.  The bound comes from the block-table width (static, so it also holds inside a CUDA graph).
     splits, part = 1, None
     if not is32 and not fma and spans.cu_q is None and H <= 64:
-        tiles = -(-(block_tables.shape[1] * block_size) // 64)
+        keys = block_tables.shape[1] * block_size
+        tiles = -(-(min(keys, window + 63) if window > 0 else keys) // 64)          # a window straddles one tile more than it fills
         chunks = -(-rank // (128 if rank <= 128 else 256))
         splits = max(1, min(tiles, 32, (2 * _sm_count()) // max(spans.num_seqs * chunks, 1)))      # whole waves: never a few CTAs over
         if splits > 1:
             part = torch.empty(spans.num_seqs * splits * 4 * H * (rank + 2), dtype=torch.float32, device=q_lat.device)   # x4: one partial per warp when H <= 16
             ops.LAUNCHES[0] += 1
-    _call("b200m_latent_attention", q_lat.data_ptr(), q_raw.data_ptr(), q_raw.shape[2], q_rot_off, cache.data_ptr(),
+    _call("b200m_latent_attention", q_lat.data_ptr(), q_raw.data_ptr(), q_raw.stride(0), q_raw.stride(1), q_rot_off, cache.data_ptr(),
           block_tables.data_ptr(), block_tables.stride(0), block_size, _p(spans.cu_q), _p(spans.cu_k), _p(spans.ctx_lens),
-          sink.data_ptr(), cos_sin.data_ptr(), cos_sin.shape[1], out.data_ptr(), n, spans.num_seqs, spans.max_q, H, rank,
-          rot_dim, scale, is32, int(fma), splits, _p(part), _stream())
+          _p(sink), cos_sin.data_ptr(), cos_sin.shape[1], out.data_ptr(), n, spans.num_seqs, spans.max_q, H, rank,
+          rot_dim, scale, int(window), int(layout), is32, int(fma), splits, _p(part), _stream())
     return out
 
 
@@ -285,10 +325,12 @@ def window_attention_splits(spans: StepSpans, max_keys: int, window: int, kv_hea
 
 def headnorm_rope_store(x: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, dim: int, vdim: int,
                         q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, v_unit_norm: bool, cos_sin: torch.Tensor | None,
-                        positions: torch.Tensor | None, slots: torch.Tensor | None, cache: torch.Tensor | None, eps: float) -> None:
+                        positions: torch.Tensor | None, slots: torch.Tensor | None, cache: torch.Tensor | None, eps: float,
+                        v_cos_sin: torch.Tensor | None = None) -> None:
     """x [n, cols] (q heads at q_off, key heads at k_off, value heads at v_off): per-head RMS norm of q and k with one weight of
     ``dim`` elements shared by the heads, pair rotation by cos_sin [positions, rope_dims] (fp32), q in place; normed, rotated keys
-    and (unit-RMS) values into cache rows [k (kv_heads * dim) | v (kv_heads * vdim)] at ``slots``."""
+    and (unit-RMS) values into cache rows [k (kv_heads * dim) | v (kv_heads * vdim)] at ``slots``.  ``v_cos_sin`` (fp32
+    [positions, v_dims]): the value pairs are turned by the token's position before the store."""
     assert x.dim() == 2 and x.stride(1) == 1
     is32 = _is32(x)
     _same(is32, q_norm, k_norm, cache)
@@ -296,10 +338,36 @@ def headnorm_rope_store(x: torch.Tensor, q_off: int, k_off: int, v_off: int, hea
     if cos_sin is not None:
         assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and positions.dtype == torch.int64
         rope_dims = cos_sin.shape[1]
+    v_dims = 0
+    if v_cos_sin is not None:
+        assert v_cos_sin.dtype == torch.float32 and v_cos_sin.is_contiguous() and positions.dtype == torch.int64
+        v_dims = v_cos_sin.shape[1]
     if cache is not None:
         assert cache.is_contiguous() and cache.shape[-1] == kv_heads * (dim + vdim) and slots.dtype == torch.int32 and slots.numel() == x.shape[0]
     _call("b200m_headnorm_rope_store", x.data_ptr(), x.stride(0), q_off, k_off, v_off, heads, kv_heads, dim, vdim, _p(q_norm), _p(k_norm),
-          int(v_unit_norm), _p(cos_sin), rope_dims, _p(positions), _p(slots), _p(cache), x.shape[0], eps, is32, _stream())
+          int(v_unit_norm), _p(cos_sin), rope_dims, _p(v_cos_sin), v_dims, _p(positions), _p(slots), _p(cache), x.shape[0], eps, is32,
+          _stream())
+
+
+def head_rotate_gate(acc: torch.Tensor, dtype, cos_sin: torch.Tensor | None = None, positions: torch.Tensor | None = None,
+                     sign: float = 1.0, layout: int = ROT_PAIRS, gate: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """acc [n, H, vdim] (any token / head strides, unit inner stride; fp32 or ``dtype``) -> [n, H * vdim] in ``dtype``: every head
+    turned by ``sign`` times the token's position (cos_sin fp32 [positions, dims]: the first ``dims`` elements of a head), then
+    multiplied by sigmoid(gate) (gate [n, H * vdim], a row-strided view)."""
+    n, H, vdim = acc.shape
+    assert acc.stride(2) == 1 and acc.dtype in (torch.float32, dtype)
+    dims = 0
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and positions.dtype == torch.int64 and positions.numel() == n
+        dims = cos_sin.shape[1]
+    assert gate is None or (gate.stride(1) == 1 and gate.shape == (n, H * vdim) and gate.dtype == dtype)
+    if out is None:
+        out = torch.empty(n, H * vdim, dtype=dtype, device=acc.device)
+    assert out.dtype == dtype and out.shape == (n, H * vdim) and out.stride(1) == 1
+    _call("b200m_head_rotate_gate", acc.data_ptr(), int(acc.dtype == torch.float32), acc.stride(0), acc.stride(1), _p(cos_sin), dims,
+          int(layout), float(sign), _p(positions), _p(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0),
+          n, H, vdim, int(dtype == torch.float32), _stream())
+    return out
 
 
 def head_mix_gate(acc: torch.Tensor, mix: torch.Tensor, gate: torch.Tensor | None, dtype, out: torch.Tensor | None = None,

@@ -43,8 +43,18 @@ def _musavik_config(raw: dict):
     return MusavikConfig(raw)
 
 
-MODELS = {"Qwen3ForCausalLM": _qwen3, "Qwen2ForCausalLM": _qwen3, "Tafopel": _tafopel, "Tipetar": _tipetar, "Musavik": _musavik}
-CONFIG_READERS = {"Tafopel": _tafopel_config, "Tipetar": _tipetar_config, "Musavik": _musavik_config}
+def _fegolorn():
+    from .fegolorn import FegolornForCausalLM
+    return FegolornForCausalLM
+
+
+def _fegolorn_config(raw: dict):
+    from .fegolorn import FegolornConfig
+    return FegolornConfig(raw)
+
+
+MODELS = {"Qwen3ForCausalLM": _qwen3, "Qwen2ForCausalLM": _qwen3, "Tafopel": _tafopel, "Tipetar": _tipetar, "Musavik": _musavik, "Fegolorn": _fegolorn}
+CONFIG_READERS = {"Tafopel": _tafopel_config, "Tipetar": _tipetar_config, "Musavik": _musavik_config, "Fegolorn": _fegolorn_config}
 
 
 def architecture_of(hf_config) -> str:
