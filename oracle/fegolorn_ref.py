@@ -84,7 +84,7 @@ def softmax_attend(scores: torch.Tensor, visible: torch.Tensor, values: torch.Te
 def attention(h, w, m, eps, pos=None):
     """Grouped-query attention: per-head RMS norm of q and k (one weight of `dim` numbers for all heads), interleaved rotation of the
     first rot.dims elements, values turned by their own position over the whole vdim and every head's sum turned back by the
-    query's position, causal softmax."""
+    query's position, causal softmax (over the last mask.size positions when the mixer has a mask)."""
     T = h.shape[0]
     H, G, d, vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     pos = torch.arange(T) if pos is None else pos
@@ -103,7 +103,11 @@ def attention(h, w, m, eps, pos=None):
     rep = H // G
     kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
     s = torch.einsum("ihd,jhd->hij", q, kk) * float(m["scale"])
-    vis = pos[None, :] <= pos[:, None]
+    dist = pos[:, None] - pos[None, :]
+    vis = dist >= 0
+    size = int((m.get("mask") or {}).get("size") or 0)
+    if size:
+        vis = vis & (dist < size)
     o = softmax_attend(s, vis, vv.transpose(0, 1))
     o = rotate(o, pos, fv, "interleaved", sign=-1.0)
     return o.reshape(T, H * vd) @ w["o"].to(F64).T
