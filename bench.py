@@ -550,11 +550,21 @@ def main():
                          "attention with mixed heads beside a gated delta rule, repeated layers) beside Tafopel, Tipetar and Qwen3 at equal size, with a "
                          "per-kernel roofline table (profiles/recurrent_bench.py); one GPU")
     ap.add_argument("--recurrent-sizes", default="w1024,w2048")
+    ap.add_argument("--gated", action="store_true",
+                    help="instead of the headline workload: prefill / decode throughput of the Fegolorn decoder (gated and scaled sublayer results, "
+                         "attention with rotated values, windowed latent attention, experts chosen by logit) beside Tafopel, Tipetar and Qwen3 at "
+                         "equal size, with a per-kernel roofline table (profiles/gated_bench.py); one GPU")
+    ap.add_argument("--gated-sizes", default="w1024,w2048")
     args = ap.parse_args()
     if args.windowed:
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
         import window_bench
         window_bench.main(["--sizes", args.windowed_sizes])
+        return
+    if args.gated:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
+        import gated_bench
+        gated_bench.main(["--sizes", args.gated_sizes])
         return
     if args.recurrent:
         sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles"))
