@@ -320,10 +320,16 @@ __global__ void __launch_bounds__(ROW_THREADS) gated_add_normed_kernel(float* __
         stf(out_next + base + c, x[base + c] * rstd2 * (w_next ? w_next[c] : 1.0f));
 }
 
-__global__ void softcap_kernel(float* __restrict__ x, int64_t n, float cap) {
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, int64_t n, float cap) {
     B200_PDL_SYNC();
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        float4 v = *reinterpret_cast<float4*>(x + i);
+        v.x = cap * tanhf(v.x / cap), v.y = cap * tanhf(v.y / cap), v.z = cap * tanhf(v.z / cap), v.w = cap * tanhf(v.w / cap);
+        *reinterpret_cast<float4*>(x + i) = v;
+    } else {
+        for (int64_t j = i; j < n && j < i + 4; ++j) x[j] = cap * tanhf(x[j] / cap);
+    }
 }
 
 }  // namespace
@@ -370,7 +376,7 @@ extern "C" int b200m_gated_add_normed_norm(float* x, const void* y, const float*
 extern "C" int b200m_softcap(float* x, int64_t n, float cap, void* stream) {
     if (!x || n < 0 || !(cap > 0.f)) return B200_EINVAL;
     if (n == 0) return B200_OK;
-    B200_LAUNCH((softcap_kernel), (unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream), x, n, cap);
+    B200_LAUNCH((softcap_kernel), (unsigned)((n + 1023) / 1024), 256, 0, static_cast<cudaStream_t>(stream), x, n, cap);
     return b200_launch_status(nullptr);
 }
 

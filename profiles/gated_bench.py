@@ -94,6 +94,12 @@ def kernel_table(size: str, peaks: dict):
             name = f"latent_attention window {win}, no sink" if win else "latent_attention causal + sink (tafopel form)"
             add(f"{name} {label}", lambda: mixops.latent_attention(q_lat, q_raw, d, cache, bt, bs, spn, None if win else sink, table, 0.07, window=win,
                                                                    layout=mixops.ROT_HALVES if win else mixops.ROT_PAIRS), nbytes, flops, "tensor")
+        if q == 1:                                          # Tafopel's form over as many keys as the window leaves visible: like for like
+            kk = min(window, k)
+            nb2 = S * (kk // bs)
+            bt2 = torch.arange(nb2, dtype=torch.int32, device=dev).view(S, -1)
+            add(f"latent_attention causal + sink (tafopel form) decode {S}x{kk}", lambda: mixops.latent_attention(q_lat, q_raw, d, cache, bt2, bs, spans(S, 1, kk),
+                sink, table, 0.07), S * kk * D * 2 + n * H * (2 * R + d + rd) * 2, S * kk * H * 2 * (D + R), "tensor")
         # ---- grouped-query attention, causal, fp32 sums (this design; the turn back follows) and the windowed form of Tipetar ----
         cache2 = rn(nblk * bs, G * 2 * d)
         qkv = rn(n, H * d)
