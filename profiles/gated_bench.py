@@ -33,12 +33,12 @@ def fegolorn_config(size: str):
     lat = {"type": "latent_attention", "mixer": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": R, "scale": 192 ** -0.5,
                                                  "mask": {"size": window}, "rot": {"dims": 64, "base": 5e4}}}
     att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                                          "rot": {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+                                          "rot": {"dims": 64, "base": 5e5, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 8192}}}}
     dense = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
     moe = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": 3 * width // (2 * top)}, "shared": {"ff": width}}
     layers = [dict(lat, mlp=dense), dict(att, mlp=moe), dict(lat, mlp=dense), dict(att, mlp=moe), dict(lat, mlp=dense), dict(att, mlp=moe)]
     layers += [dict(layers[2], weights_of=2), dict(layers[3], weights_of=3)]
-    return FegolornConfig({"architecture": "Fegolorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+    return FegolornConfig({"architecture": "Fegolorn", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 50.0,
                            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 40503, "mul_cur": 9973}},
                            "layers": layers})
 
@@ -74,7 +74,7 @@ def kernel_table(size: str, peaks: dict):
         return mixops.StepSpans(S, 1, None, None, torch.full((S,), k, dtype=torch.int32, device=dev))
 
     table = build_banded_cos_sin(rd, 8192, 5e4, None, dev)
-    vtab = build_banded_cos_sin(d, 8192, 1e6, None, dev)
+    vtab = build_banded_cos_sin(d, 8192, 5e5, None, dev)
     sink = torch.zeros(H, device=dev)
     for label, S, q, k in (("prefill 4x2048", 4, 2048, 2048), ("decode 64x4096", 64, 1, 4096)):
         nblk = S * (k // bs)
@@ -118,7 +118,7 @@ def kernel_table(size: str, peaks: dict):
     add("head_rotate_gate turn back 8192 rows", lambda: mixops.head_rotate_gate(acc, bf, vtab, pos, sign=-1.0), n * H * d * (4 + 2) + n * d * 4, 0)
     o_lat = rn(H, n, d)
     add("head_rotate_gate gate only 8192 rows", lambda: mixops.head_rotate_gate(o_lat.permute(1, 0, 2), bf, gate=gate), n * H * d * (2 + 2 + 2), 0)
-    qk_tab = build_interleaved_cos_sin(64, 8192, 1e6, None, dev)
+    qk_tab = build_interleaved_cos_sin(64, 8192, 5e5, None, dev)
     proj = rn(n, (H + 2 * G) * d)
     cache3 = torch.zeros(n, G * 2 * d, dtype=bf, device=dev)
     wq, wk = rn(d), rn(d)
@@ -143,7 +143,7 @@ def kernel_table(size: str, peaks: dict):
     gu2 = rn(n, 2 * ff)
     add("ff_act silu * up (tipetar form) 8192 rows", lambda: mixops.ff_act(gu2, mixops.FF_SILU_MUL), n * ff * 6, 0)
     logits = torch.randn(n, VOCAB, device=dev)
-    add("softcap 8192 x vocab", lambda: mixops.softcap_(logits, 30.0), n * VOCAB * 8, 0)
+    add("softcap 8192 x vocab", lambda: mixops.softcap_(logits, 50.0), n * VOCAB * 8, 0)
     z = torch.randn(n, E, device=dev)
     zero = torch.zeros(E, device=dev)
     add("moe_route_grouped, one group (top-k by logit) 8192 rows", lambda: mixops.moe_route_grouped(z, E, top, zero, 1, 1, E), n * (E * 4 + top * 8), 0)

@@ -111,7 +111,7 @@ def plain_rotated_value_attention(q, k, v, H, G, scale, base, pos_of_row):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("bs,shape", [(16, (4, 2, 32, 32)), (64, (6, 1, 64, 64)), (16, (3, 3, 10, 6))])
+@pytest.mark.parametrize("bs,shape", [(16, (4, 2, 32, 32)), (64, (10, 2, 64, 64)), (16, (3, 3, 10, 6))])
 def test_values_carry_their_position_and_the_sum_is_turned_back(dtype, bs, shape):
     """Store (value pairs turned by the token's position), causal attention, and the turn back by the query's position, with one key
     made to dominate a head: that head must return the planted value turned by (its position - the query's position) -- a key at
@@ -237,7 +237,7 @@ def _mixer(layer, dtype, width, seed, extra=0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("layer", [fh.attention(scaling=(4.0, 1.0, 4.0, 64)), fh.attention(heads=6, kv_heads=1, dim=64, vdim=32, rot_dims=16, base=1e4),
+@pytest.mark.parametrize("layer", [fh.attention(scaling=(4.0, 1.0, 4.0, 64)), fh.attention(heads=5, kv_heads=1, dim=64, vdim=32, rot_dims=16, base=1e4),
                                    fh.attention(heads=2, kv_heads=2, dim=6, vdim=10, rot_dims=6, scaling=(2.0, 2.0, 8.0, 40), window=20),
                                    fh.attention(heads=4, kv_heads=4, dim=32, vdim=64, rot_dims=0)])
 def test_attention_layer_whole_in_portions_in_batches_and_in_used_pages(dtype, layer):
@@ -261,7 +261,7 @@ def test_latent_layer_whole_in_portions_in_batches_and_in_used_pages(dtype, laye
 
 def test_band_edges_of_the_frequency_scaling():
     from nanovllm.layers.rotary_embedding import banded_frequencies
-    for dims, base, sc in ((8, 5000.0, (4.0, 1.0, 4.0, 64)), (64, 1e6, (8.0, 1.0, 4.0, 512)), (6, 40.0, (2.0, 2.0, 8.0, 40)), (16, 300.0, None)):
+    for dims, base, sc in ((8, 5000.0, (4.0, 1.0, 4.0, 64)), (64, 5e5, (4.0, 1.0, 8.0, 1024)), (6, 40.0, (2.0, 2.0, 8.0, 40)), (16, 300.0, None)):
         scaling = dict(zip(("factor", "low", "high", "original"), sc)) if sc else None
         got, want = banded_frequencies(dims, base, scaling), ref.frequencies(dims, base, scaling)
         assert torch.allclose(got, want, rtol=1e-12, atol=0)
@@ -274,8 +274,8 @@ def test_band_edges_of_the_frequency_scaling():
 def test_soft_cap():
     from nanovllm import mixops
     x = torch.linspace(-200, 200, 4001)
-    got = mixops.softcap_(x.cuda().clone(), 30.0)
-    assert rel_err(got, 30.0 * torch.tanh(x.double() / 30.0)) < 1e-6
+    got = mixops.softcap_(x.cuda().clone(), 20.0)
+    assert rel_err(got, 20.0 * torch.tanh(x.double() / 20.0)) < 1e-6
 
 
 # ---------------------------------------------------------------------------------------------------------------------------
