@@ -54,7 +54,8 @@ class FegolornConfig:
         self.num_hidden_layers = len(self.layers)
         self.max_position_embeddings = int(raw.get("max_position", max_position_embeddings))
         self.eos_token_id = raw.get("eos")
-        # runs: (layer that owns the weights, which of that layer's caches) in execution order
+        # runs: (layer that owns the weights, which of that layer's caches) in execution order; a borrowing layer runs with the owner's
+        # entry (sizes and constants), its own entry only has to agree in the mixer type
         self.runs: list[tuple[int, int]] = []
         uses: dict[int, int] = {}
         for i, layer in enumerate(self.layers):
@@ -70,9 +71,8 @@ class FegolornConfig:
                 src = int(src)
                 if not 0 <= src < i or self.layers[src].get("weights_of") is not None:
                     raise ValueError(f"layer {i}: weights_of must name an earlier layer with tensors of its own")
-                own = {k: v for k, v in layer.items() if k != "weights_of"}
-                if own != self.layers[src]:
-                    raise ValueError(f"layer {i}: its entry differs from layer {src}, whose weights it uses")
+                if layer["type"] != self.layers[src]["type"]:
+                    raise ValueError(f"layer {i}: its mixer type differs from layer {src}, whose weights it uses")
             self.runs.append((src, uses.get(src, 0)))
             uses[src] = uses.get(src, 0) + 1
         self.copies = uses                               # weight-owning layer -> caches it needs

@@ -57,7 +57,7 @@ def test_bad_configurations_are_refused():
     with pytest.raises(ValueError):
         FegolornConfig(cfg)
     cfg = fh.config_a()
-    cfg["layers"][2]["mixer"]["heads"] = 2                                   # not the entry of the layer it borrows from
+    cfg["layers"][2]["type"] = "latent_attention"                            # not the mixer of the layer it borrows from
     with pytest.raises(ValueError):
         FegolornConfig(cfg)
 
